@@ -1,0 +1,452 @@
+// Host side of librgb200.so: planning, workspace layout, TMA descriptors, launch sequence and the
+// extern "C" entry points declared in include/rgb200.h.
+//
+// Reference counterparts: make_layout / launch_quantize / launch_all / make_plan /
+// repro_gemm_fp32_ws / repro_gemm_fp32 (repro_gemm_cuda/repro_gemm.cu:390-542).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/rgb200.h"
+#include "rgb200_math.cuh"
+#include "rgb200_mma.cuh"
+#include "rgb200_prepass.cuh"
+
+namespace rgb200 {
+namespace {
+
+constexpr size_t ALIGN = 256;
+constexpr int MAX_DEVICES = 64;
+inline size_t align_up(size_t x) { return (x + ALIGN - 1) / ALIGN * ALIGN; }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+constexpr int TILE_N = 64;   // columns of C per CTA tile (the MMA is S*TILE_N wide)
+
+// ------------------------------------------------------------------------------------------
+// Planning (pure host arithmetic)
+// ------------------------------------------------------------------------------------------
+struct Layout {
+    int S, M, N, K, batch;
+    int Kp, k_blocks, min_split, split;
+    bool partial_out;          // the caller receives INT64 sums instead of C
+    bool use_partial_ws;       // K ranges are reduced through the workspace
+    size_t qa, qb, ea, eb, scratch, part;   // byte offsets into the workspace
+    size_t max_a, max_b, status;            // inside the zero-initialised scratch block
+    size_t scratch_bytes, total;
+    int algo;
+};
+
+// Largest |X| after the split: 127*128^(S-1) + 64*(128^(S-2) + ... + 1).
+double max_fixed_point(int S) {
+    double top = 127.0 * std::ldexp(1.0, 7 * (S - 1)), low = 0.0;
+    for (int t = 0; t + 1 < S; ++t) low += 64.0 * std::ldexp(1.0, 7 * t);
+    return top + low;
+}
+
+cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const rgb200_config& cfg,
+                        bool partial_out, Layout& L) {
+    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || cfg.split_k <= 0 || total_k < K) return cudaErrorInvalidValue;
+    if (cfg.slices < 1 || cfg.slices > 3) return cudaErrorInvalidValue;
+    if (cfg.algo < RGB200_ALGO_AUTO || cfg.algo > RGB200_ALGO_TENSORCORE) return cudaErrorInvalidValue;
+    const int S = cfg.slices;
+    const double d = max_fixed_point(S);
+    if ((double)total_k * d * d > std::ldexp(1.0, 62)) return cudaErrorInvalidValue;   // INT64 must hold any sum
+    if ((long long)K + BLOCK_K > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+
+    L.S = S; L.M = M; L.N = N; L.K = K; L.batch = batch;
+    L.Kp = ceil_div(K, BLOCK_K) * BLOCK_K;
+    L.k_blocks = L.Kp / BLOCK_K;
+    const int blocks_per_pass = max_k_per_pass(S) / BLOCK_K;
+    L.min_split = ceil_div(L.k_blocks, blocks_per_pass);
+    L.algo = cfg.algo == RGB200_ALGO_AUTO ? RGB200_ALGO_TENSORCORE : cfg.algo;
+    if (L.algo == RGB200_ALGO_REFERENCE) {
+        L.split = 1;            // the INT64 verification kernel never needs K ranges
+    } else {
+        L.split = cfg.split_k > L.min_split ? cfg.split_k : L.min_split;
+        if (L.split > L.k_blocks) L.split = L.k_blocks;
+    }
+    L.partial_out = partial_out;
+    if (partial_out && L.split != 1) {
+        // INT64 output for the caller: K ranges would need a second buffer; one pass covers 105k values of k
+        if (L.min_split > 1) return cudaErrorInvalidValue;
+        L.split = 1;
+    }
+    L.use_partial_ws = !partial_out && L.split > 1;
+
+    const size_t qa_bytes = (size_t)batch * S * M * L.Kp, qb_bytes = (size_t)batch * S * N * L.Kp;
+    const size_t part_bytes = L.use_partial_ws ? (size_t)L.split * batch * M * N * sizeof(long long) : 0;
+    // zero-initialised scratch block first: status word (fixed place: the first word of the workspace),
+    // then the integer column maxima of the k-strided pre-pass
+    L.status = 0;
+    L.max_a = ALIGN;
+    L.max_b = L.max_a + align_up((size_t)batch * M * sizeof(uint32_t));
+    L.scratch = 0;
+    L.scratch_bytes = L.max_b + align_up((size_t)batch * N * sizeof(uint32_t));
+    L.qa = L.scratch_bytes;
+    L.qb = L.qa + align_up(qa_bytes);
+    L.ea = L.qb + align_up(qb_bytes);
+    L.eb = L.ea + align_up((size_t)batch * M * sizeof(int));
+    L.part = L.eb + align_up((size_t)batch * N * sizeof(int));
+    L.total = L.part + align_up(part_bytes);
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-device facts, looked up once (immutable afterwards)
+// ------------------------------------------------------------------------------------------
+struct DeviceInfo { int sm_count = 0; int cc = 0; bool attrs_set = false; cudaError_t err = cudaSuccess; };
+DeviceInfo g_dev[MAX_DEVICES];
+std::once_flag g_dev_once[MAX_DEVICES];
+
+template <int S>
+cudaError_t set_kernel_attrs() {
+    return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<S, TILE_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                GemmTraits<S, TILE_N>::SMEM_BYTES);
+}
+
+cudaError_t device_info(const DeviceInfo** out) {
+    int dev;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::call_once(g_dev_once[dev], [dev] {
+        DeviceInfo& d = g_dev[dev];
+        int major = 0, minor = 0;
+        cudaError_t e2;
+        if ((e2 = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess ||
+            (e2 = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev)) != cudaSuccess ||
+            (e2 = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) {
+            d.err = e2;
+            return;
+        }
+        d.cc = major * 10 + minor;
+        if (d.cc == 100) {   // the only architecture this library carries code for
+            if ((e2 = set_kernel_attrs<1>()) != cudaSuccess || (e2 = set_kernel_attrs<2>()) != cudaSuccess ||
+                (e2 = set_kernel_attrs<3>()) != cudaSuccess) { d.err = e2; return; }
+            d.attrs_set = true;
+        }
+    });
+    if (g_dev[dev].err != cudaSuccess) return g_dev[dev].err;
+    *out = &g_dev[dev];
+    return cudaSuccess;
+}
+
+// Resolves the algorithm against the current device, as make_layout does in the reference
+// (repro_gemm_cuda/repro_gemm.cu:398-409): "not supported" when the device cannot run it.
+cudaError_t check_device(int algo, const DeviceInfo** dev) {
+    if (algo == RGB200_ALGO_TILED) return cudaErrorNotSupported;   // dp4a fallback is not part of this library
+    cudaError_t e = device_info(dev);
+    if (e != cudaSuccess) return e;
+    if ((*dev)->cc != 100) return cudaErrorNotSupported;
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA descriptors.  The driver entry point is fetched at run time so that the library loads on
+// machines without a driver (planning and the host helpers still work there).
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, int Kp, int S, int batch, int box_rows) {
+    std::call_once(g_encode_once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    });
+    if (!g_encode) return cudaErrorNotSupported;
+    // dims (fastest first): k, row, digit plane, batch.  Rows beyond `rows` read as zero.
+    cuuint64_t dims[4] = {(cuuint64_t)Kp, (cuuint64_t)rows, (cuuint64_t)S, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)Kp, (cuuint64_t)rows * Kp, (cuuint64_t)rows * Kp * S};
+    cuuint32_t box[4] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows, (cuuint32_t)S, 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(planes), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------------------------------
+// Launch sequence
+// ------------------------------------------------------------------------------------------
+// One operand through the pre-pass.  k_major: element (r, k) at src[r*K + k].
+template <int S>
+void launch_split(const float* src, bool k_major, const float* given_max, uint32_t* maxbits, int8_t* planes, int* expo,
+                  int R, int K, int Kp, int batch, long long batch_stride, cudaStream_t st) {
+    if (k_major) {
+        const bool aligned = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (batch_stride % 4 == 0);
+        if (aligned && K <= 32 * 4 * KMAJOR_CACHE_CHUNKS)
+            split_kmajor_kernel<S, 32, true><<<dim3(ceil_div(R, 8), batch), PREPASS_THREADS, 0, st>>>(
+                src, given_max, planes, expo, R, K, Kp, batch_stride);
+        else if (aligned && K <= 256 * 4 * KMAJOR_CACHE_CHUNKS)
+            split_kmajor_kernel<S, 256, true><<<dim3(R, batch), PREPASS_THREADS, 0, st>>>(
+                src, given_max, planes, expo, R, K, Kp, batch_stride);
+        else
+            split_kmajor_kernel<S, 256, false><<<dim3(R, batch), PREPASS_THREADS, 0, st>>>(
+                src, given_max, planes, expo, R, K, Kp, batch_stride);
+    } else {
+        if (given_max)
+            maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);
+        else
+            colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), ceil_div(K, COLMAX_K_PER_CTA), batch), PREPASS_THREADS, 0, st>>>(
+                src, maxbits, R, K, batch_stride);
+        split_kstrided_kernel<S><<<dim3(ceil_div(R, 32), Kp / BLOCK_K, batch), PREPASS_THREADS, 0, st>>>(
+            src, maxbits, planes, expo, R, K, Kp, batch_stride);
+    }
+}
+
+struct RunArgs {
+    const float *A, *B;
+    float* C;
+    long long* T_out;                 // INT64 output for the caller (partial mode), else null
+    const float *max_a, *max_b;       // externally reduced maxima (partial mode), else null
+    long long stride_a, stride_b, stride_c;
+    bool trans_a, trans_b;
+    char* ws;
+    cudaStream_t st;
+    const cudaEvent_t* ev;
+};
+
+template <int S>
+cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
+    using Tr = GemmTraits<S, TILE_N>;
+    auto record = [&](int i) { if (a.ev) cudaEventRecord(a.ev[i], a.st); };
+    int8_t* qa = reinterpret_cast<int8_t*>(a.ws + L.qa);
+    int8_t* qb = reinterpret_cast<int8_t*>(a.ws + L.qb);
+    int* ea = reinterpret_cast<int*>(a.ws + L.ea);
+    int* eb = reinterpret_cast<int*>(a.ws + L.eb);
+    uint32_t* max_a = reinterpret_cast<uint32_t*>(a.ws + L.max_a);
+    uint32_t* max_b = reinterpret_cast<uint32_t*>(a.ws + L.max_b);
+    int* status = reinterpret_cast<int*>(a.ws + L.status);
+    long long* part = L.use_partial_ws ? reinterpret_cast<long long*>(a.ws + L.part) : a.T_out;
+    const int e0 = -14 * (S - 1);
+
+    cudaError_t e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
+    if (e != cudaSuccess) return e;
+    record(0);
+    launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, a.st);
+    launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, a.st);
+    record(1);
+
+    if (L.algo == RGB200_ALGO_REFERENCE) {
+        gemm_int64_check_kernel<S><<<dim3(ceil_div(L.N, 16), ceil_div(L.M, 16), L.batch), dim3(16, 16), 0, a.st>>>(
+            qa, qb, ea, eb, a.C, L.M, L.N, L.Kp, a.stride_c, e0);
+        record(2);
+        record(3);
+        return cudaGetLastError();
+    }
+
+    CUtensorMap map_a, map_b;
+    if ((e = encode_planes_map(&map_a, qa, L.M, L.Kp, S, L.batch, BLOCK_M)) != cudaSuccess) return e;
+    if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, TILE_N)) != cudaSuccess) return e;
+    GemmParams P;
+    P.expo_a = ea; P.expo_b = eb;
+    P.C = part ? nullptr : a.C;
+    P.partial = part;
+    P.status = status;
+    P.M = L.M; P.N = L.N; P.batch = L.batch;
+    P.stride_c = a.stride_c;
+    P.k_blocks = L.k_blocks;
+    P.split = L.split;
+    P.m_tiles = ceil_div(L.M, BLOCK_M);
+    P.n_tiles = ceil_div(L.N, TILE_N);
+    P.e0 = e0;
+    const long long tiles = (long long)L.batch * L.split * P.m_tiles * P.n_tiles;
+    const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
+    gemm_i8_tcgen05_kernel<S, TILE_N><<<grid, GEMM_THREADS, Tr::SMEM_BYTES, a.st>>>(map_a, map_b, P);
+    record(2);
+    if (L.use_partial_ws) {
+        const size_t total = (size_t)L.batch * L.M * L.N;
+        const int blocks = (int)((total + 255) / 256 < (size_t)dev.sm_count * 16 ? (total + 255) / 256 : (size_t)dev.sm_count * 16);
+        round_partial_kernel<<<blocks, 256, 0, a.st>>>(part, L.split, total, ea, eb, nullptr, nullptr, a.C, L.M, L.N, L.batch,
+                                                        a.stride_c, e0);
+    }
+    record(3);
+    return cudaGetLastError();
+}
+
+cudaError_t dispatch(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
+    switch (L.S) {
+        case 1: return run<1>(L, a, dev);
+        case 2: return run<2>(L, a, dev);
+        case 3: return run<3>(L, a, dev);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t gemm_ws(const float* A, const float* B, float* C, int M, int N, int K, int batch, long long sa, long long sb,
+                    long long sc, const rgb200_config* cfg, void* ws, size_t ws_bytes, void* stream, void* const* events4) {
+    if (!A || !B || !C || !cfg) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = plan_layout(M, N, K, K, batch, *cfg, false, L);
+    if (e != cudaSuccess) return e;
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
+    if (!ws || ws_bytes < L.total) return cudaErrorInvalidValue;
+    if (batch > 1 && (sa < (long long)M * K || sb < (long long)K * N || sc < (long long)M * N)) return cudaErrorInvalidValue;
+    RunArgs a{A, B, C, nullptr, nullptr, nullptr, sa, sb, sc, cfg->trans_a != 0, cfg->trans_b != 0,
+              static_cast<char*>(ws), static_cast<cudaStream_t>(stream), reinterpret_cast<const cudaEvent_t*>(events4)};
+    return dispatch(L, a, *dev);
+}
+
+}  // namespace
+}  // namespace rgb200
+
+using namespace rgb200;
+
+extern "C" {
+
+void rgb200_default_config(rgb200_config* cfg) {
+    if (!cfg) return;
+    cfg->split_k = 1; cfg->tile_m = 16; cfg->tile_n = 16; cfg->tile_k = 32;
+    cfg->algo = RGB200_ALGO_AUTO; cfg->slices = 3; cfg->trans_a = 0; cfg->trans_b = 0;
+}
+
+const char* rgb200_algo_name(int algo) {
+    switch (algo) {
+        case RGB200_ALGO_AUTO: return "auto";
+        case RGB200_ALGO_REFERENCE: return "ref";
+        case RGB200_ALGO_TILED: return "tiled";
+        case RGB200_ALGO_TENSORCORE: return "tc";
+    }
+    return "?";
+}
+
+int rgb200_layout(int M, int N, int K, int batch, const rgb200_config* cfg, rgb200_layout_info* info) {
+    if (!cfg || !info) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = plan_layout(M, N, K, K, batch, *cfg, false, L);
+    if (e != cudaSuccess) return e;
+    info->k_padded = L.Kp; info->k_blocks = L.k_blocks; info->min_split = L.min_split; info->split_k = L.split;
+    info->tile_n = TILE_N;
+    info->planes_a = (size_t)batch * L.S * M * L.Kp; info->planes_b = (size_t)batch * L.S * N * L.Kp;
+    info->partial_bytes = L.total - L.part;
+    info->workspace_bytes = L.total;
+    return cudaSuccess;
+}
+
+static int make_plan_common(int M, int N, int K, long long total_k, int batch, const rgb200_config* cfg, bool partial,
+                            rgb200_plan* plan) {
+    if (!plan || !cfg) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = plan_layout(M, N, K, total_k, batch, *cfg, partial, L);
+    if (e != cudaSuccess) return e;
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
+    plan->algo = L.algo;
+    plan->split_k = L.split;
+    plan->workspace_bytes = L.total;
+    return cudaSuccess;
+}
+
+int rgb200_make_plan(int M, int N, int K, const rgb200_config* cfg, rgb200_plan* plan) {
+    return make_plan_common(M, N, K, K, 1, cfg, false, plan);
+}
+int rgb200_make_plan_batched(int M, int N, int K, int batch, const rgb200_config* cfg, rgb200_plan* plan) {
+    return make_plan_common(M, N, K, K, batch, cfg, false, plan);
+}
+int rgb200_make_plan_partial(int M, int N, int K, long long total_k, const rgb200_config* cfg, rgb200_plan* plan) {
+    return make_plan_common(M, N, K, total_k, 1, cfg, true, plan);
+}
+
+int rgb200_gemm_fp32_ws(const float* A, const float* B, float* C, int M, int N, int K, const rgb200_config* cfg,
+                        void* workspace, size_t workspace_bytes, void* stream, void* const* events4) {
+    return gemm_ws(A, B, C, M, N, K, 1, 0, 0, 0, cfg, workspace, workspace_bytes, stream, events4);
+}
+
+int rgb200_gemm_fp32_batched_ws(const float* A, const float* B, float* C, int M, int N, int K, int batch,
+                                long long stride_a, long long stride_b, long long stride_c, const rgb200_config* cfg,
+                                void* workspace, size_t workspace_bytes, void* stream, void* const* events4) {
+    return gemm_ws(A, B, C, M, N, K, batch, stride_a, stride_b, stride_c, cfg, workspace, workspace_bytes, stream, events4);
+}
+
+int rgb200_workspace_status(const void* workspace, int* status) {
+    if (!workspace || !status) return cudaErrorInvalidValue;
+    return cudaMemcpy(status, workspace, sizeof(int), cudaMemcpyDeviceToHost);   // the status word leads the workspace
+}
+
+int rgb200_gemm_fp32(const float* A, const float* B, float* C, int M, int N, int K, const rgb200_config* cfg, void* stream) {
+    rgb200_config def;
+    if (!cfg) { rgb200_default_config(&def); cfg = &def; }
+    rgb200_plan plan;
+    int rc = rgb200_make_plan(M, N, K, cfg, &plan);
+    if (rc != cudaSuccess) return rc;
+    void* ws = nullptr;
+    cudaError_t e = cudaMalloc(&ws, plan.workspace_bytes);
+    if (e != cudaSuccess) return e;
+    rc = rgb200_gemm_fp32_ws(A, B, C, M, N, K, cfg, ws, plan.workspace_bytes, stream, nullptr);
+    if (rc == cudaSuccess) rc = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (rc == cudaSuccess) {
+        int st = 0;
+        rc = rgb200_workspace_status(ws, &st);
+        if (rc == cudaSuccess && st != 0) rc = cudaErrorLaunchTimeout;
+    }
+    cudaFree(ws);
+    return rc;
+}
+
+int rgb200_absmax(const float* X, int R, int K, int k_strided, float* out, void* stream) {
+    if (!X || !out || R <= 0 || K <= 0) return cudaErrorInvalidValue;
+    const DeviceInfo* dev = nullptr;
+    cudaError_t e = check_device(RGB200_ALGO_TENSORCORE, &dev);
+    if (e != cudaSuccess) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!k_strided) {
+        rowmax_kmajor_kernel<<<ceil_div(R, PREPASS_THREADS / 32), PREPASS_THREADS, 0, st>>>(X, out, R, K);
+    } else {
+        // non-negative floats order like their bit patterns: accumulate the maxima in place as integers
+        if ((e = cudaMemsetAsync(out, 0, (size_t)R * sizeof(float), st)) != cudaSuccess) return e;
+        colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), ceil_div(K, COLMAX_K_PER_CTA), 1), PREPASS_THREADS, 0, st>>>(
+            X, reinterpret_cast<uint32_t*>(out), R, K, 0);
+    }
+    return cudaGetLastError();
+}
+
+int rgb200_gemm_partial_ws(const float* A, const float* B, const float* max_a, const float* max_b, long long* T,
+                           int M, int N, int K, long long total_k, const rgb200_config* cfg, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+    if (!A || !B || !max_a || !max_b || !T || !cfg) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = plan_layout(M, N, K, total_k, 1, *cfg, true, L);
+    if (e != cudaSuccess) return e;
+    if (L.algo == RGB200_ALGO_REFERENCE) return cudaErrorNotSupported;
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
+    if (!workspace || workspace_bytes < L.total) return cudaErrorInvalidValue;
+    RunArgs a{A, B, nullptr, T, max_a, max_b, 0, 0, 0, cfg->trans_a != 0, cfg->trans_b != 0,
+              static_cast<char*>(workspace), static_cast<cudaStream_t>(stream), nullptr};
+    return dispatch(L, a, *dev);
+}
+
+int rgb200_round_partial(const long long* T, int parts, const float* max_a, const float* max_b, float* C, int M, int N,
+                         int slices, void* stream) {
+    if (!T || !max_a || !max_b || !C || parts <= 0 || M <= 0 || N <= 0 || slices < 1 || slices > 3)
+        return cudaErrorInvalidValue;
+    const DeviceInfo* dev = nullptr;
+    cudaError_t e = check_device(RGB200_ALGO_TENSORCORE, &dev);
+    if (e != cudaSuccess) return e;
+    const size_t total = (size_t)M * N;
+    const size_t want = (total + 255) / 256, cap = (size_t)dev->sm_count * 16;
+    round_partial_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        T, parts, total, nullptr, nullptr, max_a, max_b, C, M, N, 1, (long long)total, -14 * (slices - 1));
+    return cudaGetLastError();
+}
+
+uint64_t rgb200_fnv1a64(const void* data, size_t bytes, uint64_t h) {
+    const unsigned char* p = static_cast<const unsigned char*>(data);
+    for (size_t i = 0; i < bytes; ++i) { h ^= p[i]; h *= 0x100000001b3ull; }
+    return h;
+}
+int rgb200_scale_exponent(float absmax) { return scale_exponent(absmax); }
+int rgb200_fixed_point(float x, int se, int slices) { return fixed_point(x, quant_scale(se, slices)); }
+uint32_t rgb200_round_to_float_bits(long long T, int E) { return round_to_f32_bits(T, E); }
+
+}  // extern "C"

@@ -1,0 +1,429 @@
+// tcgen05 kind::i8 mainloop with TMA-fed operands, TMEM level accumulators and the fused
+// exact-recombine-and-round epilogue (sm_100a only).
+//
+// Work decomposition.  A CTA owns one 128 x NT tile of C at a time (persistent, static round-robin
+// over tiles).  The S digit planes of an operand tile are fetched by ONE 4-D TMA box
+// (k = 128 bytes, rows, S planes, 1 batch) into 128-byte-swizzled shared memory, so the S planes of
+// the B tile sit back to back as a single K-major matrix of S*NT rows.  For every 32-wide k step the
+// issuing thread then launches S MMAs, one per A plane p:
+//        D[128 x S*NT] += A_p[128 x 32] * [B_0; B_1; ...; B_{S-1}]^T
+// with D placed at TMEM column p*NT.  Column block L of TMEM therefore accumulates every digit-plane
+// product with p + q = L ("level" L, weight 128^(2S-2-L)): S MMAs per k step cover all S^2 products
+// and A_p is read from shared memory once per step.  Only the very first k step of a tile is issued
+// as S^2 separate NT-wide MMAs, because there the "overwrite" flag differs between column blocks.
+// Level sums are exact in INT32 for max_k_per_pass(S) values of k; the host never gives one pass more.
+//
+// Epilogue: four warps read the 2S-1 level accumulators with tcgen05.ld, rebuild
+// T = sum_L level_L * 128^(2S-2-L) in INT64 and either round once to FP32 (fused; the reference's
+// write_output, repro_gemm_cuda/repro_gemm.cu:124-132, and round_to_float) or store T for a later
+// integer reduction (K ranges, K-sharded multi-GPU).
+//
+// Reference counterpart of the whole kernel: gemm_wmma_i8<S> (repro_gemm_cuda/repro_gemm.cu:280-364).
+//
+// Every wait on an mbarrier is bounded: after about two seconds the waiting role records a code in
+// the status word, raises a CTA-wide abort flag, and all roles drain and leave through the common
+// exit, which frees the CTA's TMEM.
+#pragma once
+#include <cuda.h>
+#include "rgb200_math.cuh"
+
+namespace rgb200 {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;         // bytes = int8 elements per pipeline stage and per swizzled row
+constexpr int UMMA_K = 32;           // k extent of one kind::i8 MMA
+constexpr int GEMM_THREADS = 192;    // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-5: epilogue
+constexpr int EPI_THREADS = 128;
+constexpr long long WAIT_LIMIT_CLOCKS = 4000000000ll;   // about two seconds
+
+enum : int {
+    STATUS_OK = 0,
+    STATUS_WAIT_EMPTY = 1,      // producer gave up waiting for a free pipeline stage
+    STATUS_WAIT_FULL = 2,       // MMA issuer gave up waiting for operand bytes
+    STATUS_WAIT_TMEM_EMPTY = 3, // MMA issuer gave up waiting for the epilogue to drain TMEM
+    STATUS_WAIT_TMEM_FULL = 4,  // epilogue gave up waiting for the accumulators
+    STATUS_WAIT_DRAIN = 5       // producer gave up waiting for its own copies during an abort
+};
+
+template <int S, int NT>
+struct GemmTraits {
+    static constexpr int LEVELS = 2 * S - 1;
+    static constexpr int A_PLANE_BYTES = BLOCK_M * BLOCK_K;
+    static constexpr int B_PLANE_BYTES = NT * BLOCK_K;
+    static constexpr int A_STAGE_BYTES = S * A_PLANE_BYTES;
+    static constexpr int B_STAGE_BYTES = S * B_PLANE_BYTES;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int SMEM_BUDGET = 220 * 1024;
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int TMEM_COLS_USED = LEVELS * NT;
+    static constexpr int TMEM_COLS = TMEM_COLS_USED <= 32 ? 32 : TMEM_COLS_USED <= 64 ? 64 :
+                                     TMEM_COLS_USED <= 128 ? 128 : TMEM_COLS_USED <= 256 ? 256 : 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static_assert(TMEM_COLS_USED <= 512, "level accumulators do not fit TMEM");
+    static_assert(S * NT <= 256 && (S * NT) % 16 == 0 && NT % 16 == 0, "invalid UMMA N");
+    static_assert(STAGES >= 2, "pipeline needs two stages");
+};
+
+struct GemmParams {
+    const int* expo_a;       // [batch][M]
+    const int* expo_b;       // [batch][N]
+    float* C;                // fused-rounding output, or null
+    long long* partial;      // INT64 output [split][batch][M][N], or null
+    int* status;             // one word, zero on entry
+    int M, N;
+    int batch;
+    long long stride_c;      // elements between consecutive batches of C
+    int k_blocks;            // total number of 128-wide k blocks
+    int split;               // number of K ranges
+    int m_tiles, n_tiles;
+    int e0;                  // -14 (S - 1)
+};
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+
+// Bounded wait.  Returns false after the limit or once another role has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CLOCKS) {
+                atomicCAS(status, 0, code);
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, int8 x int8 -> int32, issued by one thread.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on an mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 8 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4)      // start address
+         | (1ull << 16)                              // leading byte offset (unused with swizzled K-major)
+         | ((uint64_t)(1024 >> 4) << 32)             // stride byte offset between 8-row groups
+         | (1ull << 46)                              // descriptor version of this architecture
+         | (2ull << 61);                             // 128-byte swizzle
+}
+// Instruction descriptor: int8 x int8 -> int32, both operands K-major, dense, no saturation.
+__host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------
+// Tile schedule shared by the three roles.  Order: batch-major, then K range, then groups of 16
+// row tiles swept column tile by column tile, so CTAs running together share operand panels in L2.
+// ------------------------------------------------------------------------------------------
+struct TileCoord { int batch, z, m_blk, n_blk, kb_begin, kb_end; };
+
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& P, long long tile) {
+    const int GROUP = 16;
+    long long per_mat = (long long)P.m_tiles * P.n_tiles;
+    long long bz = tile / per_mat;
+    int t = (int)(tile - bz * per_mat);
+    TileCoord c;
+    c.batch = (int)(bz / P.split);
+    c.z = (int)(bz - (long long)c.batch * P.split);
+    int group_size = GROUP * P.n_tiles;
+    int g = t / group_size, in_g = t - g * group_size;
+    int rows_here = min(GROUP, P.m_tiles - g * GROUP);
+    c.n_blk = in_g / rows_here;
+    c.m_blk = g * GROUP + (in_g - c.n_blk * rows_here);
+    c.kb_begin = (int)((long long)P.k_blocks * c.z / P.split);
+    c.kb_end = (int)((long long)P.k_blocks * (c.z + 1) / P.split);
+    return c;
+}
+
+template <int S, int NT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const GemmParams P) {
+    using Tr = GemmTraits<S, NT>;
+    constexpr int STAGES = Tr::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    // operand stages need 1024-byte alignment for the 128-byte swizzle pattern
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + STAGES * Tr::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    const uint32_t tmem_full_bar = bar_base + 8u * (2 * STAGES);
+    const uint32_t tmem_empty_bar = bar_base + 8u * (2 * STAGES + 1);
+    const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 2);
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + STAGES * Tr::STAGE_BYTES + 8 * (2 * STAGES + 2));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + STAGES * Tr::STAGE_BYTES + 8 * (2 * STAGES + 3));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long total_tiles = (long long)P.batch * P.split * P.m_tiles * P.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(tmem_full_bar, 1);
+        mbar_init(tmem_empty_bar, EPI_THREADS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Tr::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const TileCoord tc = tile_coord(P, tile);
+                for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
+                    mbar_arrive_expect_tx(full_bar(s), Tr::STAGE_BYTES);
+                    const uint32_t sa = smem_base + s * Tr::STAGE_BYTES;
+                    tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, tc.m_blk * BLOCK_M, 0, tc.batch);
+                    tma_load_4d(sa + Tr::A_STAGE_BYTES, &tmap_b, full_bar(s), kb * BLOCK_K, tc.n_blk * NT, 0, tc.batch);
+                }
+            }
+            if (!ok) {
+                // abort: let copies that are still in flight land before the CTA gives up its shared memory
+                const uint32_t issued = it < (uint32_t)STAGES ? it : (uint32_t)STAGES;
+                for (uint32_t j = 0; j < issued; ++j) {
+                    const uint32_t i2 = it - 1 - j;
+                    long long t0 = clock64();
+                    while (!mbar_try_wait(full_bar(i2 % STAGES), (i2 / STAGES) & 1u)) {
+                        if (clock64() - t0 > WAIT_LIMIT_CLOCKS) { atomicCAS(P.status, 0, STATUS_WAIT_DRAIN); break; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
+            constexpr uint32_t IDESC_ONE = idesc_i8(BLOCK_M, NT);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
+                const TileCoord tc = tile_coord(P, tile);
+                if (!(ok = mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
+                tc_fence_after();
+                for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * Tr::STAGE_BYTES;
+                    const uint32_t sb = sa + Tr::A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        if (kb == tc.kb_begin && k == 0) {
+                            // first k step of the tile: every level block needs its own overwrite flag
+#pragma unroll
+                            for (int p = 0; p < S; ++p)
+#pragma unroll
+                                for (int q = 0; q < S; ++q)
+                                    umma_i8(tmem_base + (p + q) * NT,
+                                            smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES),
+                                            smem_desc_sw128(sb + q * Tr::B_PLANE_BYTES),
+                                            IDESC_ONE, (p != 0 && q != S - 1) ? 1u : 0u);
+                        } else {
+#pragma unroll
+                            for (int p = 0; p < S; ++p)
+                                umma_i8(tmem_base + p * NT,
+                                        smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES + k * UMMA_K),
+                                        smem_desc_sw128(sb + k * UMMA_K),
+                                        IDESC_WIDE, 1u);
+                        }
+                    }
+                    umma_commit(empty_bar(s));          // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(tmem_full_bar);     // accumulators complete
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter .. +31
+        const int row_in_tile = quarter * 32 + lane;
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
+            const TileCoord tc = tile_coord(P, tile);
+            const int row = tc.m_blk * BLOCK_M + row_in_tile;
+            const bool row_ok = row < P.M;
+            const int ea = row_ok ? __ldg(P.expo_a + (size_t)tc.batch * P.M + row) : 0;
+            const int* eb = P.expo_b + (size_t)tc.batch * P.N;
+            ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 8) {
+                __syncwarp();                          // the TMEM loads below are warp-collective
+                int lv[Tr::LEVELS][8];
+#pragma unroll
+                for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
+                tmem_ld_wait();
+                if (c0 + 8 >= NT) {
+                    // every accumulator value of this tile is in registers: hand TMEM back to the MMA warp
+                    tc_fence_before();
+                    mbar_arrive(tmem_empty_bar);
+                }
+                long long T[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    long long t = lv[0][j];
+#pragma unroll
+                    for (int L = 1; L < Tr::LEVELS; ++L) t = t * 128 + lv[L][j];
+                    T[j] = t;
+                }
+                const int col = tc.n_blk * NT + c0;
+                if (!row_ok || col >= P.N) continue;
+                if (P.partial) {
+                    long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col;
+                    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col + 8 <= P.N) {
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) *reinterpret_cast<longlong2*>(dst + j) = make_longlong2(T[j], T[j + 1]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) if (col + j < P.N) dst[j] = T[j];
+                    }
+                } else {
+                    float* dst = P.C + (size_t)tc.batch * P.stride_c + (size_t)row * P.N + col;
+                    uint32_t o[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        int e = col + j < P.N ? __ldg(eb + col + j) : 0;
+                        o[j] = round_to_f32_bits(T[j], ea + e + P.e0);
+                    }
+                    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col + 8 <= P.N) {
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(dst + 4) = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) if (col + j < P.N) dst[j] = bits_f32(o[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // common exit: every thread arrives, then the allocating warp returns the TMEM columns
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Tr::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Verification path (RGB200_ALGO_REFERENCE): the definition on CUDA cores, one thread per output,
+// digits re-assembled to the fixed-point integers and multiplied in INT64.
+// Reference counterpart: gemm_reference (repro_gemm_cuda/repro_gemm.cu:139-153).
+// grid = (ceil(N/16), ceil(M/16), batch)
+// ------------------------------------------------------------------------------------------
+template <int S>
+__global__ void gemm_int64_check_kernel(const int8_t* __restrict__ qa, const int8_t* __restrict__ qb,
+                                        const int* __restrict__ ea, const int* __restrict__ eb, float* __restrict__ C,
+                                        int M, int N, int Kp, long long stride_c, int e0) {
+    const int col = blockIdx.x * 16 + threadIdx.x, row = blockIdx.y * 16 + threadIdx.y, b = blockIdx.z;
+    if (row >= M || col >= N) return;
+    const size_t pa = (size_t)M * Kp, pb = (size_t)N * Kp;
+    const int8_t* x = qa + (size_t)b * S * pa + (size_t)row * Kp;
+    const int8_t* y = qb + (size_t)b * S * pb + (size_t)col * Kp;
+    long long t = 0;
+    for (int k = 0; k < Kp; ++k) {
+        int X = 0, Y = 0;
+#pragma unroll
+        for (int p = 0; p < S; ++p) { X = X * 128 + x[p * pa + k]; Y = Y * 128 + y[p * pb + k]; }
+        t += (long long)X * Y;
+    }
+    C[(size_t)b * stride_c + (size_t)row * N + col] =
+        bits_f32(round_to_f32_bits(t, ea[(size_t)b * M + row] + eb[(size_t)b * N + col] + e0));
+}
+
+// C = round(sum over `parts` INT64 partials); the reference's reduce_round (repro_gemm.cu:156-165).
+// partial is [parts][batch*M*N]; exponents either precomputed (ea/eb) or derived from maxima.
+__global__ void round_partial_kernel(const long long* __restrict__ partial, int parts, size_t part_stride,
+                                     const int* __restrict__ ea, const int* __restrict__ eb,
+                                     const float* __restrict__ max_a, const float* __restrict__ max_b,
+                                     float* __restrict__ C, int M, int N, int batch, long long stride_c, int e0) {
+    const size_t total = (size_t)batch * M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        long long t = 0;
+        for (int p = 0; p < parts; ++p) t += partial[(size_t)p * part_stride + i];
+        const size_t b = i / ((size_t)M * N), rc = i - b * (size_t)M * N;
+        const int r = (int)(rc / N), c = (int)(rc - (size_t)r * N);
+        const int e_r = ea ? ea[b * M + r] : scale_exponent(max_a[b * M + r]);
+        const int e_c = eb ? eb[b * N + c] : scale_exponent(max_b[b * N + c]);
+        C[b * (size_t)stride_c + (size_t)r * N + c] = bits_f32(round_to_f32_bits(t, e_r + e_c + e0));
+    }
+}
+
+}  // namespace rgb200

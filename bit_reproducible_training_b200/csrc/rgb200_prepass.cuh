@@ -1,0 +1,234 @@
+// Scale-and-split pre-pass: row/column maxima -> power-of-two scale exponents -> S int8 digit planes.
+//
+// Output layout in HBM (what the TMA descriptors of the MMA kernel read):
+//   planes[batch][S][R][Kp] int8, k contiguous ("K-major") for BOTH operands: op(A) as [M][Kp] and
+//   op(B) transposed as [N][Kp].  Kp = K rounded up to 128; the k padding is written as zeros, rows
+//   beyond R do not exist (TMA zero-fills them).  expo[batch][R] int32 holds the scale exponents.
+// Algorithmic traffic: (4 + S) bytes per input element (+ 4 per row).
+//
+// Reference counterparts: quantize_kmajor / quantize_kstrided (repro_gemm_cuda/repro_gemm.cu:54-121),
+// which read every operand twice with scalar loads and one block per row or 32 rows.
+#pragma once
+#include "rgb200_math.cuh"
+
+namespace rgb200 {
+
+constexpr int PREPASS_THREADS = 256;
+constexpr int KMAJOR_CACHE_CHUNKS = 16;   // float4 chunks a thread keeps in registers
+
+__device__ __forceinline__ float abs4max(float m, float4 v) {
+    return fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+// Quantise four consecutive k values and store them as one 32-bit word per digit plane.
+template <int S>
+__device__ __forceinline__ void store_quad(float4 v, const QuantScale& q, int8_t* plane0, size_t plane_stride, size_t idx) {
+    int d[4][S];
+    split_digits<S>(fixed_point(v.x, q), d[0]);
+    split_digits<S>(fixed_point(v.y, q), d[1]);
+    split_digits<S>(fixed_point(v.z, q), d[2]);
+    split_digits<S>(fixed_point(v.w, q), d[3]);
+#pragma unroll
+    for (int p = 0; p < S; ++p) {
+        uint32_t w = (uint32_t)(d[0][p] & 0xFF) | ((uint32_t)(d[1][p] & 0xFF) << 8) |
+                     ((uint32_t)(d[2][p] & 0xFF) << 16) | ((uint32_t)(d[3][p] & 0xFF) << 24);
+        *reinterpret_cast<uint32_t*>(plane0 + p * plane_stride + idx) = w;
+    }
+}
+
+// Max over the TPR threads that share a row.  TPR == 32: one warp per row.  TPR == 256: one CTA per row.
+template <int TPR>
+__device__ __forceinline__ float row_group_max(float m, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (TPR > 32) {
+        int w = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) red[w] = m;
+        __syncthreads();
+        m = red[0];
+#pragma unroll
+        for (int i = 1; i < TPR / 32; ++i) m = fmaxf(m, red[i]);
+    }
+    return m;
+}
+
+// ---------------------------------------------------------------------------------------------
+// k-contiguous operand: element (r, k) at src[r*K + k]   (A without trans_a, B with trans_b).
+// One read of the operand: a row group keeps its row in registers between the max and the split
+// (VEC path, K % 4 == 0, K <= 64 * TPR); otherwise the row is read again (it is still in L2).
+// grid = (ceil(R / (256 / TPR)), batch)
+// ---------------------------------------------------------------------------------------------
+template <int S, int TPR, bool VEC>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ given_max,
+                    int8_t* __restrict__ planes, int* __restrict__ expo,
+                    int R, int K, int Kp, long long src_batch_stride) {
+    __shared__ float red[PREPASS_THREADS / 32];
+    const int rows_per_cta = PREPASS_THREADS / TPR;
+    const int row = blockIdx.x * rows_per_cta + threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int b = blockIdx.y;
+    const bool live = row < R;                 // TPR == 256: uniform over the CTA; TPR == 32: over the warp
+    const size_t plane_stride = (size_t)R * Kp;
+    const float* a = src + (size_t)b * src_batch_stride + (size_t)(live ? row : 0) * K;
+    int8_t* out = planes + (size_t)b * S * plane_stride + (size_t)(live ? row : 0) * Kp;
+    if (TPR == 32 && !live) return;            // whole warp leaves together; no CTA-wide barrier on this path
+
+    float m = 0.0f;
+    if (VEC) {
+        const float4* a4 = reinterpret_cast<const float4*>(a);
+        const int nq = K >> 2, nqp = Kp >> 2;
+        float4 v[KMAJOR_CACHE_CHUNKS];
+#pragma unroll
+        for (int i = 0; i < KMAJOR_CACHE_CHUNKS; ++i) {
+            int c = t + i * TPR;
+            v[i] = (live && c < nq) ? __ldg(a4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            m = abs4max(m, v[i]);
+        }
+        m = row_group_max<TPR>(m, red);
+        if (!live) return;
+        if (given_max) m = given_max[(size_t)b * R + row];
+        const int e = scale_exponent(m);
+        if (t == 0) expo[(size_t)b * R + row] = e;
+        const QuantScale q = quant_scale(e, S);
+#pragma unroll
+        for (int i = 0; i < KMAJOR_CACHE_CHUNKS; ++i) {
+            int c = t + i * TPR;
+            if (c < nqp) store_quad<S>(v[i], q, out, plane_stride, (size_t)c * 4);   // c >= nq: zeros (k padding)
+        }
+    } else {
+        if (live && !given_max)
+            for (int k = t; k < K; k += TPR) m = fmaxf(m, fabsf(__ldg(a + k)));
+        m = row_group_max<TPR>(m, red);
+        if (!live) return;
+        if (given_max) m = given_max[(size_t)b * R + row];
+        const int e = scale_exponent(m);
+        if (t == 0) expo[(size_t)b * R + row] = e;
+        const QuantScale q = quant_scale(e, S);
+        for (int k = t * 4; k < Kp; k += TPR * 4) {
+            float4 v;
+            v.x = k + 0 < K ? __ldg(a + k + 0) : 0.f;
+            v.y = k + 1 < K ? __ldg(a + k + 1) : 0.f;
+            v.z = k + 2 < K ? __ldg(a + k + 2) : 0.f;
+            v.w = k + 3 < K ? __ldg(a + k + 3) : 0.f;
+            store_quad<S>(v, q, out, plane_stride, (size_t)k);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// k-strided operand: element (r, k) at src[k*R + r]   (B without trans_b, A with trans_a).
+// Pass 1: column maxima over K with an integer atomicMax (|x| >= 0 orders like its bit pattern,
+// so the result is exact and order-free).  maxbits[batch][R] must be zero on entry.
+// grid = (ceil(R / 128), ceil(K / 256), batch), block = 256 threads = 32 column groups x 8 k-rows.
+// ---------------------------------------------------------------------------------------------
+constexpr int COLMAX_K_PER_CTA = 256;
+
+__global__ void __launch_bounds__(PREPASS_THREADS)
+colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ maxbits, int R, int K,
+                       long long src_batch_stride) {
+    __shared__ float red[8][128 + 4];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int b = blockIdx.z;
+    const float* s = src + (size_t)b * src_batch_stride;
+    const int r0 = blockIdx.x * 128 + tx * 4;
+    const int k_lo = blockIdx.y * COLMAX_K_PER_CTA;
+    const int k_hi = min(K, k_lo + COLMAX_K_PER_CTA);
+    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+    const bool vec = (R & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) & 15) == 0);
+    if (vec) {
+        if (r0 < R)
+            for (int k = k_lo + ty; k < k_hi; k += 8) {
+                float4 v = __ldg(reinterpret_cast<const float4*>(s + (size_t)k * R + r0));
+                m0 = fmaxf(m0, fabsf(v.x)); m1 = fmaxf(m1, fabsf(v.y));
+                m2 = fmaxf(m2, fabsf(v.z)); m3 = fmaxf(m3, fabsf(v.w));
+            }
+    } else {
+        for (int k = k_lo + ty; k < k_hi; k += 8) {
+            const float* p = s + (size_t)k * R + r0;
+            if (r0 + 0 < R) m0 = fmaxf(m0, fabsf(__ldg(p + 0)));
+            if (r0 + 1 < R) m1 = fmaxf(m1, fabsf(__ldg(p + 1)));
+            if (r0 + 2 < R) m2 = fmaxf(m2, fabsf(__ldg(p + 2)));
+            if (r0 + 3 < R) m3 = fmaxf(m3, fabsf(__ldg(p + 3)));
+        }
+    }
+    red[ty][tx * 4 + 0] = m0; red[ty][tx * 4 + 1] = m1; red[ty][tx * 4 + 2] = m2; red[ty][tx * 4 + 3] = m3;
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        float m = red[0][threadIdx.x];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i][threadIdx.x]);
+        int r = blockIdx.x * 128 + threadIdx.x;
+        if (r < R && m > 0.0f) atomicMax(maxbits + (size_t)b * R + r, f32_bits(m));
+    }
+}
+
+// Row maxima of a k-contiguous operand, written as floats (the K-sharded path's first step).
+// One warp per row.  grid = ceil(R / 8).
+__global__ void __launch_bounds__(PREPASS_THREADS)
+rowmax_kmajor_kernel(const float* __restrict__ src, float* __restrict__ out, int R, int K) {
+    const int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5);
+    if (row >= R) return;
+    const float* a = src + (size_t)row * K;
+    float m = 0.f;
+    for (int k = threadIdx.x & 31; k < K; k += 32) m = fmaxf(m, fabsf(__ldg(a + k)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if ((threadIdx.x & 31) == 0) out[row] = m;
+}
+
+// Pass 2 for the k-strided operand: a 32 (r) x 128 (k) tile is read with r contiguous, transposed
+// through shared memory and written with k contiguous, 128 bytes per row and plane.
+// grid = (ceil(R / 32), Kp / 128, batch)
+template <int S>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict__ maxbits,
+                      int8_t* __restrict__ planes, int* __restrict__ expo,
+                      int R, int K, int Kp, long long src_batch_stride) {
+    __shared__ __align__(16) float tile[32][128 + 4];   // [r][k]
+    __shared__ int e_sh[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = blockIdx.z;
+    const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 128;
+    const float* s = src + (size_t)b * src_batch_stride;
+    const size_t plane_stride = (size_t)R * Kp;
+    int8_t* out = planes + (size_t)b * S * plane_stride;
+
+    if (threadIdx.x < 32) {
+        int r = r0 + threadIdx.x;
+        int e = r < R ? scale_exponent(bits_f32(maxbits[(size_t)b * R + r])) : 0;
+        e_sh[threadIdx.x] = e;
+        if (r < R && blockIdx.y == 0) expo[(size_t)b * R + r] = e;
+    }
+    // load: warp w takes k = k0 + w, w + 8, ...; lanes run along r (one 128-byte row segment)
+    {
+        const int r = r0 + lane;
+#pragma unroll 4
+        for (int kk = warp; kk < 128; kk += 8) {
+            int k = k0 + kk;
+            tile[lane][kk] = (r < R && k < K) ? __ldg(s + (size_t)k * R + r) : 0.0f;
+        }
+    }
+    __syncthreads();
+    // split: warp w takes rows w, w + 8, ...; lanes run along k in groups of four
+#pragma unroll
+    for (int rr = warp; rr < 32; rr += 8) {
+        int r = r0 + rr;
+        if (r >= R) continue;
+        const QuantScale q = quant_scale(e_sh[rr], S);
+        float4 v = *reinterpret_cast<const float4*>(&tile[rr][lane * 4]);
+        store_quad<S>(v, q, out, plane_stride, (size_t)r * Kp + k0 + lane * 4);
+    }
+}
+
+// Turns float maxima (as exchanged between ranks) into the bit form split_kstrided_kernel reads.
+__global__ void maxima_to_bits_kernel(const float* __restrict__ in, uint32_t* __restrict__ out, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = f32_bits(fmaxf(in[i], 0.0f));
+}
+__global__ void bits_to_maxima_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = bits_f32(in[i]);
+}
+
+}  // namespace rgb200

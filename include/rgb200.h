@@ -1,0 +1,134 @@
+/*
+ * rgb200 - C ABI of the B200-native integer-exact FP32 GEMM  (librgb200.so)
+ *
+ * C[M,N] = op(A)[M,K] * op(B)[K,N], FP32 in and out, row-major, with the output bits defined by
+ * the reference project's "repro_gemm" arithmetic alone: every row of op(A) and column of op(B)
+ * gets a power-of-two scale, every input is rounded once to a 7*S-bit fixed-point integer, the
+ * integer dot products are formed exactly, and the exact sum is rounded once to FP32.
+ *
+ * Every entry point takes plain pointers and sizes.  All device work is enqueued on the stream
+ * that is passed in (a cudaStream_t cast to void*; NULL = the default stream).  Return values are
+ * cudaError_t codes as int (0 = success, 1 = cudaErrorInvalidValue, 801 = cudaErrorNotSupported).
+ *
+ * File:line citations name the interface of the reference project that each declaration stands
+ * in for (paths inside that project).
+ */
+#ifndef RGB200_H
+#define RGB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* repro_gemm_cuda/repro_gemm.cuh:25-30  enum class Algo */
+enum {
+    RGB200_ALGO_AUTO = 0,        /* the tcgen05 tensor-core path */
+    RGB200_ALGO_REFERENCE = 1,   /* one thread per output, INT64 on CUDA cores; slow, for verification */
+    RGB200_ALGO_TILED = 2,       /* the reference's dp4a fallback: not built here, always "not supported" */
+    RGB200_ALGO_TENSORCORE = 3   /* same as AUTO */
+};
+
+/* repro_gemm_cuda/repro_gemm.cuh:32-41  struct Config (same fields, same order, same defaults) */
+typedef struct rgb200_config {
+    int split_k;   /* >= 1; a hint that never changes the output bits */
+    int tile_m;    /* ignored, as in the reference */
+    int tile_n;    /* ignored */
+    int tile_k;    /* ignored */
+    int algo;      /* RGB200_ALGO_* */
+    int slices;    /* S, 1..3 */
+    int trans_a;   /* 0: A is M x K row-major; 1: A is K x M row-major (use A^T) */
+    int trans_b;   /* 0: B is K x N row-major; 1: B is N x K row-major (use B^T) */
+} rgb200_config;
+
+/* repro_gemm_cuda/repro_gemm.cuh:44-48  struct Plan */
+typedef struct rgb200_plan {
+    int algo;                /* resolved, never AUTO */
+    int split_k;             /* effective number of K ranges */
+    size_t workspace_bytes;  /* what the _ws entry points need */
+} rgb200_plan;
+
+/* Fills *cfg with the reference's defaults (split_k 1, tiles 16/16/32, AUTO, 3 slices, no transposes). */
+void rgb200_default_config(rgb200_config* cfg);
+
+/* repro_gemm_cuda/repro_gemm.cuh:53  make_plan
+ * 1 (invalid value): null plan, M/N/K/split_k <= 0, slices outside 1..3, K too large for an exact
+ * INT64 sum at this S.  801 (not supported): the algorithm cannot run on the current device. */
+int rgb200_make_plan(int M, int N, int K, const rgb200_config* cfg, rgb200_plan* plan);
+
+/* repro_gemm_cuda/repro_gemm.cuh:60-66  repro_gemm_fp32_ws
+ * Asynchronous and allocation-free.  A, B, C and workspace are device pointers; workspace holds at
+ * least plan.workspace_bytes (256-byte aligned).  events4, if not NULL, points to four cudaEvent_t
+ * recorded before the split pre-pass, after it, after the MMA kernel and after the final step. */
+int rgb200_gemm_fp32_ws(const float* A, const float* B, float* C, int M, int N, int K,
+                        const rgb200_config* cfg, void* workspace, size_t workspace_bytes,
+                        void* stream, void* const* events4);
+
+/* repro_gemm_cuda/repro_gemm.cuh:69-73  repro_gemm_fp32
+ * Convenience form: allocates the workspace, runs, synchronises the stream, frees.  Also reports
+ * (as 702, launch timeout) a kernel that gave up on one of its bounded waits. */
+int rgb200_gemm_fp32(const float* A, const float* B, float* C, int M, int N, int K,
+                     const rgb200_config* cfg, void* stream);
+
+/* repro_gemm_cuda/repro_gemm.cuh:75  algo_name  ("auto", "ref", "tiled", "tc") */
+const char* rgb200_algo_name(int algo);
+
+/* Strided-batched form: `batch` independent products, matrix b of each operand starting
+ * stride_x * b elements after the first.  The reference lists batched attention GEMMs as pending
+ * (gpt2_ops_suite/gpt2_ops_suite.cu:543-548); semantics are those of `batch` calls of
+ * repro_gemm_fp32_ws (repro_gemm_cuda/repro_gemm.cuh:60). */
+int rgb200_make_plan_batched(int M, int N, int K, int batch, const rgb200_config* cfg, rgb200_plan* plan);
+int rgb200_gemm_fp32_batched_ws(const float* A, const float* B, float* C, int M, int N, int K, int batch,
+                                long long stride_a, long long stride_b, long long stride_c,
+                                const rgb200_config* cfg, void* workspace, size_t workspace_bytes,
+                                void* stream, void* const* events4);
+
+/* K-sharded operation (one K range per GPU).  The reference has no multi-GPU path
+ * (README.md:29-30 lists it as still needed); these three calls split its single-GPU sequence
+ * repro_gemm_cuda/repro_gemm.cu:451-489 at the two points where ranks must exchange data.
+ *
+ *  1. rgb200_absmax: out[r] = max over k of |op(X)[r,k]| for this rank's K range.  `k_strided` = 1 when
+ *     k is the slow index of the stored matrix (B without trans_b, A with trans_a).  Ranks then take
+ *     an element-wise max of `out` (exact, order-free) so every rank derives the same scales.
+ *  2. rgb200_gemm_partial_ws: with the global maxima given, writes the exact INT64 sums T[M,N] over
+ *     this rank's K range.  Ranks then add their T (integer addition: exact in any order).
+ *  3. rgb200_round_partial: C = the single rounding of (sum of `parts` stacked T) * 2^(eA + eB - 14(S-1)),
+ *     the job of reduce_round at repro_gemm_cuda/repro_gemm.cu:156-165.
+ * K is this rank's extent; total_k (the sum over ranks) is checked against the INT64 bound. */
+int rgb200_absmax(const float* X, int R, int K, int k_strided, float* out, void* stream);
+int rgb200_make_plan_partial(int M, int N, int K, long long total_k, const rgb200_config* cfg, rgb200_plan* plan);
+int rgb200_gemm_partial_ws(const float* A, const float* B, const float* max_a, const float* max_b,
+                           long long* T, int M, int N, int K, long long total_k, const rgb200_config* cfg,
+                           void* workspace, size_t workspace_bytes, void* stream);
+int rgb200_round_partial(const long long* T, int parts, const float* max_a, const float* max_b, float* C,
+                         int M, int N, int slices, void* stream);
+
+/* Call after the stream has been synchronised.  *status = 0 if the last run that used this workspace
+ * completed, else the code a kernel left when one of its bounded waits expired (it then stopped
+ * without hanging; the output is incomplete).  The reference reports kernel failures only through
+ * cudaGetLastError (repro_gemm_cuda/repro_gemm.cu:527); this is the same channel for that one case. */
+int rgb200_workspace_status(const void* workspace, int* status);
+
+/* Host-side helpers matching repro_gemm_cuda/repro_test_util.h:20-24 (FNV-1a-64 over raw bytes) and
+ * repro_gemm_cuda/repro_gemm_math.cuh:59,74,96 (the three scalar functions, computed by this
+ * library's own host code so callers can cross-check them without a GPU). */
+uint64_t rgb200_fnv1a64(const void* data, size_t bytes, uint64_t h);
+int rgb200_scale_exponent(float absmax);
+int rgb200_fixed_point(float x, int scale_exponent, int slices);
+uint32_t rgb200_round_to_float_bits(long long T, int E);
+
+/* Pure host planning (no device query): padded K, number of 128-wide K blocks, the K-range count
+ * the INT32 accumulators force, and the workspace size, for tests and capacity planning.
+ * Mirrors the arithmetic of make_layout at repro_gemm_cuda/repro_gemm.cu:390-439. */
+typedef struct rgb200_layout_info {
+    int k_padded, k_blocks, min_split, split_k, tile_n;
+    size_t planes_a, planes_b, partial_bytes, workspace_bytes;
+} rgb200_layout_info;
+int rgb200_layout(int M, int N, int K, int batch, const rgb200_config* cfg, rgb200_layout_info* info);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RGB200_H */

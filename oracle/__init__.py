@@ -1,0 +1,190 @@
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE: ctypes access to the CPU checkers.
+
+``liboracle.so`` is the plain-C restatement of the reference's integer-exact GEMM definition
+(``oracle/oracle.c``); ``_ref/librepro_ref.so`` is the reference's own ``cpu_gemm``
+(repro_gemm_cuda/repro_gemm_cpu.h:25) compiled from its sources.  Only the tests, the smoke check
+and the CPU-baseline legs of the benchmark may import this module; the shipped package never does.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "liboracle.so")
+_REF = os.path.join(_HERE, "_ref", "librepro_ref.so")
+
+FNV_OFFSET = 0xCBF29CE484222325
+
+
+def build(force=False):
+    """Compile the checkers with oracle/Makefile (the reference build only where its sources exist)."""
+    if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True, capture_output=True)
+    if force or not os.path.exists(_REF):
+        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB)
+        fp, ip, i64p = C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_int64)
+        L.orc_scale_exponent.argtypes = [C.c_float]
+        L.orc_scale_exponent.restype = C.c_int
+        L.orc_fixed_point.argtypes = [C.c_float, C.c_int, C.c_int]
+        L.orc_fixed_point.restype = C.c_int
+        L.orc_round_to_float_bits.argtypes = [C.c_int64, C.c_int]
+        L.orc_round_to_float_bits.restype = C.c_uint32
+        L.orc_digits.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_int8)]
+        L.orc_gemm.argtypes = [fp, fp, fp] + [ip] * 7
+        L.orc_gemm.restype = C.c_int
+        L.orc_gemm_partial.argtypes = [fp, fp, i64p, fp, fp] + [ip] * 9
+        L.orc_gemm_partial.restype = C.c_int
+        L.orc_absmax.argtypes = [fp, fp, ip, ip, ip]
+        L.orc_round_partials.argtypes = [i64p, ip, fp, fp, fp, ip, ip, ip]
+        L.orc_fnv1a64.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64]
+        L.orc_fnv1a64.restype = C.c_uint64
+        st = C.POINTER(C.c_uint64)
+        L.orc_fill_uniform_pm1.argtypes = [fp, C.c_size_t, st]
+        L.orc_fill_normal.argtypes = [fp, C.c_size_t, C.c_double, st]
+        L.orc_fill_u01.argtypes = [fp, C.c_size_t, C.c_double, st]
+        L.orc_fill_wide.argtypes = [fp, C.c_size_t, C.c_int, C.c_int, st]
+        L.orc_fill_wide_mixed.argtypes = [fp, C.c_size_t, C.c_int, C.c_int, st]
+        L.orc_fill_prob_rows.argtypes = [fp, C.c_size_t, C.c_size_t, st]
+        _lib = L
+    return _lib
+
+
+_ref = None
+
+
+def ref():
+    """The reference's own CPU implementation, or None where it has not been built."""
+    global _ref
+    if _ref is None and os.path.exists(_REF):
+        R = C.CDLL(_REF)
+        fp = C.POINTER(C.c_float)
+        R.ref_cpu_gemm.argtypes = [fp, fp, fp] + [C.c_int] * 6
+        R.ref_scale_exponent.argtypes = [C.c_float]
+        R.ref_scale_exponent.restype = C.c_int
+        R.ref_fixed_point.argtypes = [C.c_float, C.c_int, C.c_int]
+        R.ref_fixed_point.restype = C.c_int
+        R.ref_round_to_float.argtypes = [C.c_int64, C.c_int]
+        R.ref_round_to_float.restype = C.c_float
+        _ref = R
+    return _ref
+
+
+def default_threads():
+    env = os.environ.get("REPRO_CPU_THREADS")
+    return int(env) if env else (os.cpu_count() or 1)
+
+
+def gemm(A, B, M, N, K, ta=False, tb=False, S=3, threads=None):
+    """C[M,N] = op(A) op(B) by the restated definition (float32 numpy in, float32 [M,N] out)."""
+    A, pa = _f32(A)
+    B, pb = _f32(B)
+    assert A.size == M * K and B.size == K * N
+    out = np.empty((M, N), dtype=np.float32)
+    rc = lib().orc_gemm(pa, pb, out.ctypes.data_as(C.POINTER(C.c_float)), M, N, K, int(ta), int(tb), S,
+                        threads or default_threads())
+    if rc != 0:
+        raise MemoryError("oracle gemm: allocation failed")
+    return out
+
+
+def ref_gemm(A, B, M, N, K, ta=False, tb=False, S=3):
+    """The same product by the reference's own cpu_gemm (needs oracle/_ref)."""
+    R = ref()
+    if R is None:
+        raise RuntimeError("oracle/_ref/librepro_ref.so has not been built")
+    A, pa = _f32(A)
+    B, pb = _f32(B)
+    assert A.size == M * K and B.size == K * N
+    out = np.empty((M, N), dtype=np.float32)
+    R.ref_cpu_gemm(pa, pb, out.ctypes.data_as(C.POINTER(C.c_float)), M, N, K, int(ta), int(tb), S)
+    return out
+
+
+def absmax(src, R, K, k_strided):
+    src, ps = _f32(src)
+    out = np.empty(R, dtype=np.float32)
+    lib().orc_absmax(ps, out.ctypes.data_as(C.POINTER(C.c_float)), R, K, int(k_strided))
+    return out
+
+
+def gemm_partial(A, B, maxA, maxB, M, N, K, ta, tb, S, k0, k1, threads=None):
+    """Exact int64 sums over k in [k0, k1) with scales fixed by the given whole-K maxima."""
+    A, pa = _f32(A)
+    B, pb = _f32(B)
+    maxA, pma = _f32(maxA)
+    maxB, pmb = _f32(maxB)
+    T = np.empty((M, N), dtype=np.int64)
+    rc = lib().orc_gemm_partial(pa, pb, T.ctypes.data_as(C.POINTER(C.c_int64)), pma, pmb, M, N, K, int(ta), int(tb), S,
+                                k0, k1, threads or default_threads())
+    if rc != 0:
+        raise MemoryError("oracle gemm_partial: allocation failed")
+    return T
+
+
+def round_partials(T, maxA, maxB, M, N, S):
+    T = np.ascontiguousarray(T, dtype=np.int64).reshape(-1, M, N)
+    maxA, pma = _f32(maxA)
+    maxB, pmb = _f32(maxB)
+    out = np.empty((M, N), dtype=np.float32)
+    lib().orc_round_partials(T.ctypes.data_as(C.POINTER(C.c_int64)), T.shape[0], pma, pmb,
+                             out.ctypes.data_as(C.POINTER(C.c_float)), M, N, S)
+    return out
+
+
+def fnv1a64(arr, h=FNV_OFFSET):
+    """FNV-1a-64 of the raw bytes of a numpy array, chained from ``h``."""
+    arr = np.ascontiguousarray(arr)
+    return int(lib().orc_fnv1a64(arr.ctypes.data, arr.nbytes, h))
+
+
+def hexhash(arr, h=FNV_OFFSET):
+    return "%016x" % fnv1a64(arr, h)
+
+
+class Rng:
+    """SplitMix64 stream with the reference's derived draws; fills are sequential like its tools."""
+
+    def __init__(self, seed):
+        self.state = C.c_uint64(seed)
+
+    def _fill(self, fn, n, *args):
+        out = np.empty(n, dtype=np.float32)
+        fn(out.ctypes.data_as(C.POINTER(C.c_float)), n, *args, C.byref(self.state))
+        return out
+
+    def uniform_pm1(self, n):
+        return self._fill(lib().orc_fill_uniform_pm1, n)
+
+    def normal(self, n, scale=1.0):
+        return self._fill(lib().orc_fill_normal, n, scale)
+
+    def u01(self, n, scale=1.0):
+        return self._fill(lib().orc_fill_u01, n, scale)
+
+    def wide(self, n, elo, ehi):
+        return self._fill(lib().orc_fill_wide, n, elo, ehi)
+
+    def wide_mixed(self, n, elo=-20, ehi=20):
+        return self._fill(lib().orc_fill_wide_mixed, n, elo, ehi)
+
+    def prob_rows(self, rows, cols):
+        out = np.empty(rows * cols, dtype=np.float32)
+        lib().orc_fill_prob_rows(out.ctypes.data_as(C.POINTER(C.c_float)), rows, cols, C.byref(self.state))
+        return out
