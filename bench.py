@@ -1,0 +1,292 @@
+"""Benchmark of the integer-exact FP32 GEMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode rows|ksplit]
+
+One step = one full pass of the hot path (split pre-pass, int8 MMA mainloop, fused rounding
+epilogue) over one 4096 x 4096 x 4096, S = 3 GEMM with the wide-dynamic-range synthetic inputs.
+With N > 1 GPUs (torchrun, one rank per GPU) the default mode shards rows of A: every rank owns a
+4096-row block of a (4096 N) x 4096 x 4096 product and the whole B; no collective is on the data
+path (weak scaling).  --mode ksplit instead gives every rank a 4096-wide K range of a
+4096 x 4096 x (4096 N) product and reduces the exact INT64 partial sums with an NCCL all-reduce.
+
+Prints one JSON line (rank 0).  `value` is 2 M N K / time summed over ranks with the inputs
+resident in HBM; `e2e` repeats the measurement through the host-buffer call (pinned host memory,
+copies inside the timed region).  --impl reference times the reference's CPU implementation
+(oracle/_ref, built from the reference's sources) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SIZE = 4096
+SLICES = 3
+METRIC = "bit-exact FP32 GEMM TFLOP/s (2MNK/t), S=3, 4096^3"
+NOMINAL_INT8_TOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one MMA-kernel launch at this workload, from the
+# ncu capture summarised in profiles/; None until a capture has been taken
+MMA_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=5)
+        sm, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_run(steps, warmup, sample_rows):
+    """Times the reference's cpu_gemm (or the restated oracle if that library is absent) on the first
+    `sample_rows` rows of A against the whole B.  Returns (TFLOP/s, seconds per step, info)."""
+    import oracle
+    from bit_reproducible_training_b200 import fixtures as fx
+    c = fx.config3(SIZE)[0]
+    A = c["A"][:sample_rows * SIZE]
+    B = c["B"]
+    use_ref = oracle.ref() is not None
+    fn = (lambda: oracle.ref_gemm(A, B, sample_rows, SIZE, SIZE, False, False, SLICES)) if use_ref else \
+         (lambda: oracle.gemm(A, B, sample_rows, SIZE, SIZE, False, False, SLICES))
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    tflops = 2.0 * sample_rows * SIZE * SIZE / dt / 1e12
+    info = {"value": tflops, "unit": "TFLOP/s", "cores": oracle.default_threads(),
+            "kind": "reference" if use_ref else "port",
+            "sample": "rows 0..%d of A times all of B (%dx%dx%d of the %d^3 workload), %d step(s)" %
+                      (sample_rows - 1, sample_rows, SIZE, SIZE, SIZE, steps)}
+    return tflops, dt, info
+
+
+def reference_arm(args, rank):
+    if rank != 0:
+        return
+    tflops, dt, info = cpu_reference_run(args.steps, min(args.warmup, 1), 512)
+    line = {"impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": {"workload": "4096x4096x4096 S=3 wide-dynamic-range GEMM; CPU sample: " + info["sample"]},
+            "cpu_baseline": info,
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="rows", choices=["rows", "ksplit"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--check", action="store_true", help="also compare the output hash with the golden value")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from bit_reproducible_training_b200 import fixtures as fx
+    from bit_reproducible_training_b200 import repro_gemm as rg
+    from bit_reproducible_training_b200 import sharded
+
+    args.warmup = max(args.warmup, 3)
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    M = N = K = SIZE
+    S = SLICES
+    # the same synthetic operands on every rank: the values do not influence the time
+    c = fx.config3(SIZE)[0]
+    hA = torch.from_numpy(c["A"]).pin_memory()
+    hB = torch.from_numpy(c["B"]).pin_memory()
+    hC = torch.empty(M * N, dtype=torch.float32).pin_memory()
+    dA, dB = hA.cuda(), hB.cuda()
+    dC = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    cfg = rg.Config(slices=S)
+    rc, plan = rg.make_plan(M, N, K, cfg)
+    if rc != 0:
+        raise rg.ReproGemmError(rc, "make_plan")
+    ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")     # 4x the 126 MB L2
+    stream = torch.cuda.current_stream()
+    stage_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    for evs in stage_ev:
+        for e in evs:
+            e.record()          # creates the handles the library records into
+    ks = sharded.KSplitState(M, N, K, world, cfg, dA, dB) if (args.mode == "ksplit" and world > 1) else None
+
+    def step(events=None):
+        if ks is not None:
+            ks.step(dC)
+            return
+        rc = rg.repro_gemm_fp32_ws(dA, dB, dC, M, N, K, cfg, ws, stream=stream, stage_events=events)
+        if rc != 0:
+            raise rg.ReproGemmError(rc, "repro_gemm_fp32_ws")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        flush.zero_()
+        step()
+    barrier()
+    if rg.workspace_status(ws) != 0:
+        raise RuntimeError("a kernel reported an expired wait (status %d)" % rg.workspace_status(ws))
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()                       # L2 flush between timed iterations, outside the timed brackets
+        t_ev[i][0].record()
+        step(stage_ev[i])
+        t_ev[i][1].record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    step_ms = [a.elapsed_time(b) for a, b in t_ev]
+    total_ms = sum(step_ms)
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    flops_step = 2.0 * M * N * K * world
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+
+    # per-stage durations from the four events the library records inside each call
+    stages = None
+    if ks is None:
+        pre = [e[0].elapsed_time(e[1]) for e in stage_ev]
+        mma = [e[1].elapsed_time(e[2]) for e in stage_ev]
+        fin = [e[2].elapsed_time(e[3]) for e in stage_ev]
+        stages = {"prepass_ms": statistics.mean(pre), "mma_ms": statistics.mean(mma), "final_ms": statistics.mean(fin)}
+
+    # ---------------- end to end: host buffers in, host buffer out, copies inside the timed region
+    e2e_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for _ in range(2):
+        rg.gemm_host(hA, hB, hC, dA, dB, dC, M, N, K, cfg, ws, stream)
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()
+        e2e_ev[i][0].record()
+        rg.gemm_host(hA, hB, hC, dA, dB, dC, M, N, K, cfg, ws, stream)
+        e2e_ev[i][1].record()
+    barrier()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_ev)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = flops_step / (e2e_ms / args.steps * 1e-3) / 1e12
+
+    check = None
+    if args.check and rank == 0:
+        with open(os.path.join(ROOT, "tests", "golden", "gemm_hashes.json")) as f:
+            want = [r for r in json.load(f) if r["name"] == "c3.4096" and r["S"] == S][0]["out_hash"]
+        check = ("%016x" % rg.fnv1a64(hC.numpy())) == want
+
+    if rank == 0:
+        peaks = measured_peaks()
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                "config": {"workload": "C=A.B fp32, M=N=K=4096 per GPU, S=3 int8 slices, wide-dynamic-range inputs "
+                                       "(1% zeros, 0.1% subnormals), seed 3",
+                           "sharding": "none" if world == 1 else ("rows of A, no collective" if ks is None else
+                                                                  "K ranges, NCCL int64 all-reduce"),
+                           "l2": "512 MiB buffer written between timed iterations (L2 flush)"},
+                "clocks": clocks,
+                "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 4,
+                        "d2h_bytes_per_step": M * N * 4},
+                "gpu_launches": (4 if ks is None else ks.launches_per_step) * args.steps}
+        if stages:
+            mma_ops = 2.0 * S * S * M * N * K
+            achieved = mma_ops / (stages["mma_ms"] * 1e-3) / 1e12
+            peak = 2.0 * peaks["bf16_tflops"]
+            line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                                "frac": achieved / peak, "traffic": MMA_DRAM_TRAFFIC_BYTES,
+                                "kernel": "gemm_i8_tcgen05_kernel<3,64>",
+                                "note": "int8 ops/s of the slice-pair MMAs (2*S^2*M*N*K per launch); peak = 2 x the %s "
+                                        "dense bf16 cuBLAS rate (kind::i8 issues at twice the bf16 rate)" % peaks["source"],
+                                "frac_of_nominal_int8_4500": achieved / NOMINAL_INT8_TOPS}
+            line["stages"] = stages
+            pre_bytes = (4.0 + S) * (M * K + N * K) + 4.0 * (M + N)
+            line["prepass_roofline"] = {"bound": "hbm", "achieved": pre_bytes / (stages["prepass_ms"] * 1e-3) / 1e9,
+                                        "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                        "frac": pre_bytes / (stages["prepass_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        if check is not None:
+            line["output_matches_golden"] = check
+        if world == 1 and not args.no_cpu_baseline:
+            _, _, info = cpu_reference_run(2, 1, 1024)
+            line["cpu_baseline"] = info
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

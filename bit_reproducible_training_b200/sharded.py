@@ -1,0 +1,90 @@
+"""Multi-GPU forms of the GEMM, one process per GPU over torch.distributed.
+
+The reference is single-GPU (its README lists a deterministic multi-GPU reduction as still needed,
+README.md:29-30).  Because the products are exact integers until the single final rounding, the
+work can be cut in two ways without changing one output bit:
+
+* rows of A: every rank owns a block of rows of op(A) and the whole of B.  Row scales and every
+  T[i, j] are formed entirely on one rank, so there is no collective on the data path.
+* K ranges: every rank owns a K range of both operands.  Ranks first agree on the row and column
+  maxima (an element-wise max, exact and order-free), then form exact INT64 partial sums with the
+  shared scales, add them with an integer all-reduce (associative, cannot overflow: |T| <= 2^62 is
+  enforced for the whole K) and round once.
+
+The arithmetic backend is a parameter so the sharding logic can be exercised on CPU ranks (gloo)
+by the tests; the default backend is the CUDA library.
+"""
+import torch
+import torch.distributed as dist
+
+from . import repro_gemm as rg
+
+
+def shard_range(n, world, rank):
+    """Contiguous, balanced range of `n` items owned by `rank` out of `world`."""
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+class CudaBackend:
+    """The shipped arithmetic: librgb200.so on the current CUDA device."""
+
+    def gemm(self, A, B, M, N, K, cfg):
+        return rg.gemm(A, B, M, N, K, cfg.trans_a, cfg.trans_b, cfg.slices, cfg.split_k, cfg.algo)
+
+    def absmax(self, X, R, K, k_strided):
+        return rg.absmax(X, R, K, k_strided)
+
+    def gemm_partial(self, A, B, max_a, max_b, M, N, K, total_k, cfg):
+        return rg.gemm_partial(A, B, max_a, max_b, M, N, K, total_k, cfg)
+
+    def round_partial(self, T, max_a, max_b, M, N, slices):
+        return rg.round_partial(T, max_a, max_b, M, N, slices)
+
+
+def gemm_row_sharded(A_rows, B, m_local, N, K, cfg, backend=None, gather_group=None):
+    """This rank's rows of C = op(A) op(B).  A_rows holds rows [lo, hi) of op(A) (for trans_a the
+    stored matrix is K x m_local).  With `gather_group` the row blocks are all-gathered into the
+    full C (plain FP32 copy; sizes may differ per rank)."""
+    backend = backend or CudaBackend()
+    C_rows = backend.gemm(A_rows, B, m_local, N, K, cfg)
+    if gather_group is None:
+        return C_rows
+    world = dist.get_world_size(gather_group)
+    sizes = [torch.zeros(1, dtype=torch.int64, device=C_rows.device) for _ in range(world)]
+    dist.all_gather(sizes, torch.tensor([m_local], dtype=torch.int64, device=C_rows.device), group=gather_group)
+    parts = [torch.empty((int(s.item()), N), dtype=torch.float32, device=C_rows.device) for s in sizes]
+    if len({p.shape[0] for p in parts}) == 1:
+        dist.all_gather(parts, C_rows.contiguous(), group=gather_group)
+    else:
+        for src, p in enumerate(parts):           # ragged row blocks: one broadcast per owner
+            if src == dist.get_rank(gather_group):
+                p.copy_(C_rows)
+            dist.broadcast(p, src=dist.get_global_rank(gather_group, src), group=gather_group)
+    return torch.cat(parts, dim=0)
+
+
+def gemm_k_sharded(A_k, B_k, M, N, k_local, total_k, cfg, group=None, backend=None):
+    """Full C on every rank from per-rank K ranges.  A_k is this rank's [M, k_local] block of op(A)
+    (stored k_local x M when trans_a), B_k its [k_local, N] block of op(B) (N x k_local when trans_b)."""
+    backend = backend or CudaBackend()
+    max_a = backend.absmax(A_k, M, k_local, cfg.trans_a)          # k is the slow index iff trans_a
+    max_b = backend.absmax(B_k, N, k_local, not cfg.trans_b)      # ... iff B is stored K x N
+    dist.all_reduce(max_a, op=dist.ReduceOp.MAX, group=group)
+    dist.all_reduce(max_b, op=dist.ReduceOp.MAX, group=group)
+    T = backend.gemm_partial(A_k, B_k, max_a, max_b, M, N, k_local, total_k, cfg)
+    dist.all_reduce(T, op=dist.ReduceOp.SUM, group=group)
+    return backend.round_partial(T, max_a, max_b, M, N, cfg.slices)
+
+
+class KSplitState:
+    """Benchmark helper: this rank's operands are one K range of an M x N x (K * world) product."""
+    launches_per_step = 8   # row max, column max, split A, maxima->bits + split B, MMA, rounding (+ the memset)
+
+    def __init__(self, M, N, K, world, cfg, dA, dB):
+        self.M, self.N, self.K, self.world, self.cfg, self.dA, self.dB = M, N, K, world, cfg, dA, dB
+
+    def step(self, dC):
+        out = gemm_k_sharded(self.dA, self.dB, self.M, self.N, self.K, self.K * self.world, self.cfg)
+        dC.copy_(out.reshape(-1))

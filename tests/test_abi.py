@@ -1,0 +1,136 @@
+"""The C-ABI library: loads without a GPU, exports everything include/rgb200.h declares, and its
+host-side planning and scalar helpers behave like the reference's (no kernels are launched here)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from bit_reproducible_training_b200 import _lib, build
+from bit_reproducible_training_b200 import fixtures as fx
+from bit_reproducible_training_b200 import repro_gemm as rg
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    build.build()
+    return _lib.lib()
+
+
+def test_library_exports_every_declared_symbol(L):
+    header = open(os.path.join(ROOT, "include", "rgb200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    names = set(re.findall(r"\b(rgb200_[a-z0-9_]+)\s*\(", header))
+    assert len(names) >= 17
+    for n in sorted(names):
+        assert hasattr(L, n), "librgb200.so does not export %s" % n
+
+
+def test_cxx_shim_declares_the_reference_surface():
+    shim = open(os.path.join(ROOT, "include", "repro_gemm.cuh")).read()
+    for needle in ("namespace repro_gemm", "enum class Algo", "struct Config", "struct Plan", "make_plan",
+                   "repro_gemm_fp32_ws", "repro_gemm_fp32", "algo_name", "MAX_SLICES"):
+        assert needle in shim, needle
+
+
+def test_default_config_matches_reference_defaults(L):
+    c = _lib.Config()
+    L.rgb200_default_config(C.byref(c))
+    assert (c.split_k, c.tile_m, c.tile_n, c.tile_k, c.algo, c.slices, c.trans_a, c.trans_b) == (1, 16, 16, 32, 0, 3, 0, 0)
+    d = rg.Config().c()
+    assert bytes(c) == bytes(d)
+
+
+def test_algo_names(L):
+    assert [rg.algo_name(a) for a in (rg.Algo.Auto, rg.Algo.Reference, rg.Algo.Tiled, rg.Algo.TensorCore)] == \
+        ["auto", "ref", "tiled", "tc"]
+
+
+def layout(L, M, N, K, batch=1, **kw):
+    info = _lib.LayoutInfo()
+    c = rg.Config(**kw).c()
+    rc = L.rgb200_layout(M, N, K, batch, C.byref(c), C.byref(info))
+    return rc, info
+
+
+def test_layout_rejects_bad_arguments(L):
+    assert layout(L, 0, 4, 4)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, -1, 4)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 0)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 4, split_k=0)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 4, slices=0)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 4, slices=4)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 4, batch=0)[0] == rg.cudaErrorInvalidValue
+
+
+def test_k_bound_for_exact_int64(L):
+    """K * max|X|^2 <= 2^62: S = 3 allows K up to about a million (reference: repro_gemm.cu:394-396)."""
+    assert layout(L, 8, 8, 1056000, slices=3)[0] == 0
+    assert layout(L, 8, 8, 1057000, slices=3)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 8, 8, 50_000_000, slices=2)[0] == 0
+
+
+def test_split_is_clamped_and_raised(L):
+    rc, info = layout(L, 64, 64, 7, split_k=16)
+    assert rc == 0 and (info.k_padded, info.k_blocks, info.split_k) == (128, 1, 1)
+    rc, info = layout(L, 133, 77, 301, split_k=64)
+    assert rc == 0 and (info.k_blocks, info.split_k) == (3, 3)
+    rc, info = layout(L, 128, 128, 4096, split_k=7)
+    assert rc == 0 and info.split_k == 7 and info.partial_bytes >= 7 * 128 * 128 * 8
+    # one INT32 pass holds 105516 values of k at S = 3 (824 blocks of 128): longer K is cut automatically
+    rc, info = layout(L, 128, 128, 824 * 128, slices=3)
+    assert rc == 0 and info.min_split == 1 and info.split_k == 1 and info.partial_bytes == 0
+    rc, info = layout(L, 128, 128, 824 * 128 + 1, slices=3)
+    assert rc == 0 and info.min_split == 2 and info.split_k == 2
+    rc, info = layout(L, 128, 128, 1032 * 128 + 1, slices=2)
+    assert rc == 0 and info.min_split == 2
+    rc, info = layout(L, 128, 128, 1040 * 128 + 1, slices=1)
+    assert rc == 0 and info.min_split == 2
+
+
+def test_level_sums_fit_int32_for_one_pass():
+    # worst-case per-k magnitude of one level, from the digit ranges |d0| <= 127, |d_{p>0}| <= 64
+    worst = {1: 127 * 127, 2: max(127 * 127, 2 * 127 * 64, 64 * 64), 3: 2 * 127 * 64 + 64 * 64}
+    blocks = {1: 1040, 2: 1032, 3: 824}
+    for S in (1, 2, 3):
+        assert blocks[S] * 128 * worst[S] <= 2 ** 31 - 1
+        assert (blocks[S] + 1) * 128 * worst[S] > 2 ** 31 - 1
+
+
+def test_workspace_size_covers_planes(L):
+    rc, info = layout(L, 4096, 4096, 4096)
+    assert rc == 0
+    assert info.planes_a == 3 * 4096 * 4096 and info.planes_b == 3 * 4096 * 4096
+    assert info.workspace_bytes >= info.planes_a + info.planes_b + 2 * 4096 * 4
+    assert info.workspace_bytes < info.planes_a + info.planes_b + (1 << 20)
+    rc, b = layout(L, 1024, 1024, 64, batch=96)
+    assert rc == 0 and b.planes_a == 96 * 3 * 1024 * 128
+
+
+def test_host_scalar_helpers_match_reference_vectors(L, scalar_vectors):
+    for bits, want in scalar_vectors["scale_exponent"]:
+        assert L.rgb200_scale_exponent(float(np.uint32(bits).view(np.float32))) == want
+    for bits, se, x1, x2, x3 in scalar_vectors["fixed_point"]:
+        x = float(np.uint32(bits).view(np.float32))
+        assert [L.rgb200_fixed_point(x, se, S) for S in (1, 2, 3)] == [x1, x2, x3]
+    for T, E, want in scalar_vectors["round_to_float"]:
+        assert L.rgb200_round_to_float_bits(T, E) == want, (T, E)
+
+
+def test_fnv_matches_reference_input_hashes(L):
+    op = [o for o in fx.suite_gemm_ops(1024) if o[0] == "attn_proj.fwd"][0]
+    A, B = fx.suite_inputs(op)
+    assert "%016x" % rg.fnv1a64(B, rg.fnv1a64(A)) == "46dd3a91b61dc793"
+
+
+def test_plan_without_a_device_fails_cleanly(L):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    rc, plan = rg.make_plan(64, 64, 64)
+    assert rc != 0 and plan is None
+    rc, _ = rg.make_plan(64, 64, 64, rg.Config(algo=rg.Algo.Tiled))
+    assert rc == rg.cudaErrorNotSupported
