@@ -1,0 +1,162 @@
+"""Behaviour of the entry points themselves: error codes, stage events, the convenience call,
+the verification algorithm, and the K-range / row-block building blocks of the multi-GPU modes
+(emulated on one GPU by running the shards one after another)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from bit_reproducible_training_b200 import fixtures as fx
+from bit_reproducible_training_b200 import repro_gemm as rg
+from bit_reproducible_training_b200 import sharded
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def test_error_codes():
+    M, N, K = 64, 48, 200
+    A, B = dev(fx.Rng(1).normal(M * K)), dev(fx.Rng(2).normal(K * N))
+    out = torch.empty(M * N, device="cuda")
+    cfg = rg.Config()
+    rc, plan = rg.make_plan(M, N, K, cfg)
+    assert rc == 0 and plan.algo == rg.Algo.TensorCore and plan.split_k == 1
+    ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+    assert rg.repro_gemm_fp32_ws(None, B, out, M, N, K, cfg, ws) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, None, out, M, N, K, cfg, ws) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, None, M, N, K, cfg, ws) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, out, M, N, K, cfg, ws[:plan.workspace_bytes - 1]) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, out, M, N, K, cfg, None) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, out, M, N, K, rg.Config(slices=4), ws) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, out, M, N, K, rg.Config(split_k=0), ws) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, out, 0, N, K, cfg, ws) == rg.cudaErrorInvalidValue
+    assert rg.repro_gemm_fp32_ws(A, B, out, M, N, K, rg.Config(algo=rg.Algo.Tiled), ws) == rg.cudaErrorNotSupported
+    assert rg.make_plan(M, N, 2_000_000, rg.Config(slices=3))[0] == rg.cudaErrorInvalidValue
+    # a good call still works afterwards (no sticky error state)
+    assert rg.repro_gemm_fp32_ws(A, B, out, M, N, K, cfg, ws) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError):
+        rg.gemm(torch.zeros(M * K), torch.zeros(K * N), M, N, K)       # CPU tensors: there is no CPU path
+
+
+def test_stage_events_are_recorded_in_order():
+    n = 1024
+    c = fx.config3(n)[0]
+    A, B = dev(c["A"]), dev(c["B"])
+    out = torch.empty(n * n, device="cuda")
+    for split in (1, 4):
+        cfg = rg.Config(split_k=split)
+        rc, plan = rg.make_plan(n, n, n, cfg)
+        ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for e in ev:
+            e.record()
+        assert rg.repro_gemm_fp32_ws(A, B, out, n, n, n, cfg, ws, stage_events=ev) == 0
+        torch.cuda.synchronize()
+        t = [ev[i].elapsed_time(ev[i + 1]) for i in range(3)]
+        assert t[0] > 0 and t[1] > 0 and t[2] >= 0
+        if split > 1:
+            assert t[2] > 0          # the integer reduction + rounding kernel ran as the final step
+
+
+def test_convenience_call_and_custom_stream():
+    M, N, K = 200, 120, 900
+    A, B = fx.hash_tool_inputs("weights", M, N, K)
+    want = oracle.gemm(A, B, M, N, K)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    assert rg.repro_gemm_fp32(dev(A), dev(B), out, M, N, K) == 0
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    s = torch.cuda.Stream()
+    dA, dB = dev(A), dev(B)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        got = rg.gemm(dA, dB, M, N, K)
+    s.synchronize()
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_verification_algorithm_equals_tensor_core_path():
+    M, N, K = 333, 257, 1500
+    A, B = fx.hash_tool_inputs("stress", M, N, K)
+    for S in (1, 2, 3):
+        ref = rg.gemm(dev(A), dev(B), M, N, K, slices=S, algo=rg.Algo.Reference)
+        tc = rg.gemm(dev(A), dev(B), M, N, K, slices=S, algo=rg.Algo.TensorCore)
+        assert torch.equal(ref.view(torch.int32), tc.view(torch.int32))
+
+
+def test_long_k_is_cut_into_int32_safe_ranges():
+    """K beyond one INT32 pass (105516 at S = 3): the planner raises the K-range count by itself
+    and the result still equals the oracle.  Inputs of maximal magnitude make the level sums as
+    large as they can get."""
+    M, N, K = 130, 70, 824 * 128 + 300
+    A = np.ones(M * K, dtype=np.float32)
+    B = np.ones(K * N, dtype=np.float32)
+    A[::7] = -1.0
+    rc, plan = rg.make_plan(M, N, K, rg.Config())
+    assert rc == 0 and plan.split_k == 2
+    got = rg.gemm(dev(A), dev(B), M, N, K).cpu().numpy()
+    want = oracle.gemm(A, B, M, N, K)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # one full pass at the bound, worst-case digits (all +-127 * 128^2 ... ) stays exact too
+    K1 = 824 * 128
+    A1 = np.full(8 * K1, 127.0, dtype=np.float32)
+    B1 = np.full(K1 * 8, -127.0, dtype=np.float32)
+    got = rg.gemm(dev(A1), dev(B1), 8, 8, K1).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), oracle.gemm(A1, B1, 8, 8, K1).view(np.uint32))
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_k_ranges_emulated_on_one_gpu(ta, tb):
+    """The three K-shard calls, run for 3 uneven ranges one after another: maxima are combined with
+    an element-wise max, the INT64 partials with an integer sum, and one rounding gives the bits of
+    the unsharded product."""
+    M, N, K = 150, 90, 1000
+    A, B = fx.hash_tool_inputs("stress", M, N, K)
+    want = oracle.gemm(A, B, M, N, K)
+    Am, Bm = A.reshape(M, K), B.reshape(K, N)
+    cuts = [(0, 130), (130, 131), (131, 1000)]
+    shards = []
+    for lo, hi in cuts:
+        a = Am[:, lo:hi]
+        b = Bm[lo:hi]
+        shards.append((dev(a.T if ta else a), dev(b.T if tb else b), hi - lo))
+    cfg = rg.Config(trans_a=ta, trans_b=tb)
+    max_a = torch.stack([rg.absmax(a, M, k, ta) for a, _, k in shards]).amax(0)
+    max_b = torch.stack([rg.absmax(b, N, k, not tb) for _, b, k in shards]).amax(0)
+    assert np.array_equal(max_a.cpu().numpy(), oracle.absmax(A, M, K, False))
+    assert np.array_equal(max_b.cpu().numpy(), oracle.absmax(B, N, K, True))
+    parts = [rg.gemm_partial(a, b, max_a, max_b, M, N, k, K, cfg) for a, b, k in shards]
+    for (lo, hi), T in zip(cuts, parts):
+        wantT = oracle.gemm_partial(A, B, max_a.cpu().numpy(), max_b.cpu().numpy(), M, N, K, False, False, 3, lo, hi)
+        assert np.array_equal(T.cpu().numpy(), wantT)
+    got = rg.round_partial(torch.stack(parts).sum(0), max_a, max_b, M, N, 3)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    stacked = rg.round_partial(torch.stack(parts), max_a, max_b, M, N, 3)        # the library sums the stack itself
+    assert torch.equal(stacked.view(torch.int32), got.view(torch.int32))
+
+
+def test_row_blocks_emulated_on_one_gpu():
+    M, N, K = 500, 130, 640
+    A, B = fx.hash_tool_inputs("wide", M, N, K)
+    want = oracle.gemm(A, B, M, N, K)
+    dB = dev(B)
+    blocks = []
+    for r in range(3):
+        lo, hi = sharded.shard_range(M, 3, r)
+        blocks.append(sharded.gemm_row_sharded(dev(A[lo * K:hi * K]), dB, hi - lo, N, K, rg.Config()))
+    got = torch.cat(blocks).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_repeated_runs_and_workspace_reuse_are_bit_stable():
+    n = 768
+    g = fx.Rng(9)
+    A, B = dev(g.wide(n * n, -30, 30)), dev(g.normal(n * n))
+    first = rg.gemm(A, B, n, n, n)
+    other = rg.gemm(B, A, n, n, n)      # a different problem through the same cached workspace
+    for _ in range(5):
+        assert torch.equal(rg.gemm(A, B, n, n, n).view(torch.int32), first.view(torch.int32))
+    assert not torch.equal(other, first)
