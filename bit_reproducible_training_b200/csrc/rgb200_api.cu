@@ -183,15 +183,21 @@ void launch_split(const float* src, bool k_major, const float* given_max, uint32
                   int R, int K, int Kp, int batch, long long batch_stride, cudaStream_t st) {
     if (k_major) {
         const bool aligned = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (batch_stride % 4 == 0);
-        if (aligned && K <= 32 * 4 * KMAJOR_CACHE_CHUNKS)
-            split_kmajor_kernel<S, 32, true><<<dim3(ceil_div(R, 8), batch), PREPASS_THREADS, 0, st>>>(
+        const int nq = Kp / 4;     // float4 chunks per padded row
+#define RGB_KMAJOR(TPR, CH)                                                                                   \
+        split_kmajor_kernel<S, TPR, CH, true><<<dim3(ceil_div(R, PREPASS_THREADS / TPR), batch), PREPASS_THREADS, 0, st>>>( \
+            src, given_max, planes, expo, R, K, Kp, batch_stride)
+        if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS)
+            split_kmajor_kernel<S, 256, 1, false><<<dim3(R, batch), PREPASS_THREADS, 0, st>>>(
                 src, given_max, planes, expo, R, K, Kp, batch_stride);
-        else if (aligned && K <= 256 * 4 * KMAJOR_CACHE_CHUNKS)
-            split_kmajor_kernel<S, 256, true><<<dim3(R, batch), PREPASS_THREADS, 0, st>>>(
-                src, given_max, planes, expo, R, K, Kp, batch_stride);
-        else
-            split_kmajor_kernel<S, 256, false><<<dim3(R, batch), PREPASS_THREADS, 0, st>>>(
-                src, given_max, planes, expo, R, K, Kp, batch_stride);
+        else if (nq <= 32 * 2) RGB_KMAJOR(32, 2);
+        else if (nq <= 32 * 4) RGB_KMAJOR(32, 4);
+        else if (nq <= 64 * 4) RGB_KMAJOR(64, 4);
+        else if (nq <= 128 * 4) RGB_KMAJOR(128, 4);
+        else if (nq <= 256 * 4) RGB_KMAJOR(256, 4);
+        else if (nq <= 256 * 8) RGB_KMAJOR(256, 8);
+        else RGB_KMAJOR(256, 16);
+#undef RGB_KMAJOR
     } else {
         if (given_max)
             maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);

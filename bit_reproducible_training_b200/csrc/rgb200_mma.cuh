@@ -13,10 +13,11 @@
 // as S^2 separate NT-wide MMAs, because there the "overwrite" flag differs between column blocks.
 // Level sums are exact in INT32 for max_k_per_pass(S) values of k; the host never gives one pass more.
 //
-// Epilogue: four warps read the 2S-1 level accumulators with tcgen05.ld, rebuild
-// T = sum_L level_L * 128^(2S-2-L) in INT64 and either round once to FP32 (fused; the reference's
-// write_output, repro_gemm_cuda/repro_gemm.cu:124-132, and round_to_float) or store T for a later
-// integer reduction (K ranges, K-sharded multi-GPU).
+// Epilogue: eight warps read the 2S-1 level accumulators with tcgen05.ld and rebuild
+// T = sum_L level_L * 128^(2S-2-L) in INT64 registers (one 32x32->64 multiply-add per level), then
+// hand TMEM back to the MMA warp at once, so the next tile's mainloop runs while the epilogue rounds
+// once to FP32 (fused; the reference's write_output, repro_gemm_cuda/repro_gemm.cu:124-132, and
+// round_to_float) or stores T for a later integer reduction (K ranges, K-sharded multi-GPU).
 //
 // Reference counterpart of the whole kernel: gemm_wmma_i8<S> (repro_gemm_cuda/repro_gemm.cu:280-364).
 //
@@ -32,8 +33,9 @@ namespace rgb200 {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 128;         // bytes = int8 elements per pipeline stage and per swizzled row
 constexpr int UMMA_K = 32;           // k extent of one kind::i8 MMA
-constexpr int GEMM_THREADS = 192;    // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-5: epilogue
-constexpr int EPI_THREADS = 128;
+constexpr int EPI_WARPS = 8;         // two warps per TMEM lane quarter, each taking half of the tile's columns
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int GEMM_THREADS = 64 + EPI_THREADS;   // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, then the epilogue
 constexpr long long WAIT_LIMIT_CLOCKS = 4000000000ll;   // about two seconds
 
 enum : int {
@@ -155,6 +157,12 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -306,8 +314,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        constexpr int CPT = NT / 2;                    // columns per thread
+        static_assert(CPT % 16 == 0, "epilogue reads TMEM sixteen columns at a time");
         const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter .. +31
+        const int half = (warp - 2) >> 2;              // which half of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
         uint32_t tile_it = 0;
         bool ok = true;
@@ -321,53 +332,57 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 8) {
-                __syncwarp();                          // the TMEM loads below are warp-collective
-                int lv[Tr::LEVELS][8];
+            // phase 1: accumulators -> exact INT64 sums in registers, then release TMEM
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * CPT;
+            long long T[CPT];
 #pragma unroll
-                for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
+            for (int c0 = 0; c0 < CPT; c0 += 16) {
+                int lv[Tr::LEVELS][16];
+#pragma unroll
+                for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld16(t_row + L * NT + c0, lv[L]);
                 tmem_ld_wait();
-                if (c0 + 8 >= NT) {
-                    // every accumulator value of this tile is in registers: hand TMEM back to the MMA warp
-                    tc_fence_before();
-                    mbar_arrive(tmem_empty_bar);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    long long t = lv[Tr::LEVELS - 1][j];
+#pragma unroll
+                    for (int L = Tr::LEVELS - 2; L >= 0; --L)
+                        t += (long long)lv[L][j] * (long long)(1 << (7 * (Tr::LEVELS - 1 - L)));
+                    T[c0 + j] = t;
                 }
-                long long T[8];
+            }
+            tc_fence_before();
+            mbar_arrive(tmem_empty_bar);
+            // phase 2: one rounding per output (or the raw sums), overlapped with the next tile's MMAs
+            const int col0 = tc.n_blk * NT + half * CPT;
+            if (!row_ok || col0 >= P.N) continue;
+            if (P.partial) {
+                long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col0;
+                const bool vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col0 + CPT <= P.N;
+                if (vec) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    long long t = lv[0][j];
+                    for (int j = 0; j < CPT; j += 2) *reinterpret_cast<longlong2*>(dst + j) = make_longlong2(T[j], T[j + 1]);
+                } else {
 #pragma unroll
-                    for (int L = 1; L < Tr::LEVELS; ++L) t = t * 128 + lv[L][j];
-                    T[j] = t;
+                    for (int j = 0; j < CPT; ++j) if (col0 + j < P.N) dst[j] = T[j];
                 }
-                const int col = tc.n_blk * NT + c0;
-                if (!row_ok || col >= P.N) continue;
-                if (P.partial) {
-                    long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col;
-                    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col + 8 <= P.N) {
+            } else {
+                float* dst = P.C + (size_t)tc.batch * P.stride_c + (size_t)row * P.N + col0;
+                const int ebase = ea + P.e0;
+                const bool vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col0 + CPT <= P.N;
+                if (vec) {
 #pragma unroll
-                        for (int j = 0; j < 8; j += 2) *reinterpret_cast<longlong2*>(dst + j) = make_longlong2(T[j], T[j + 1]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) if (col + j < P.N) dst[j] = T[j];
+                    for (int j = 0; j < CPT; j += 4) {
+                        uint4 o;
+                        o.x = round_to_f32_bits(T[j + 0], ebase + __ldg(eb + col0 + j + 0));
+                        o.y = round_to_f32_bits(T[j + 1], ebase + __ldg(eb + col0 + j + 1));
+                        o.z = round_to_f32_bits(T[j + 2], ebase + __ldg(eb + col0 + j + 2));
+                        o.w = round_to_f32_bits(T[j + 3], ebase + __ldg(eb + col0 + j + 3));
+                        *reinterpret_cast<uint4*>(dst + j) = o;
                     }
                 } else {
-                    float* dst = P.C + (size_t)tc.batch * P.stride_c + (size_t)row * P.N + col;
-                    uint32_t o[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        int e = col + j < P.N ? __ldg(eb + col + j) : 0;
-                        o[j] = round_to_f32_bits(T[j], ea + e + P.e0);
-                    }
-                    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col + 8 <= P.N) {
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-                        *reinterpret_cast<uint4*>(dst + 4) = make_uint4(o[4], o[5], o[6], o[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) if (col + j < P.N) dst[j] = bits_f32(o[j]);
-                    }
+                    for (int j = 0; j < CPT; ++j)
+                        if (col0 + j < P.N) dst[j] = bits_f32(round_to_f32_bits(T[j], ebase + __ldg(eb + col0 + j)));
                 }
             }
         }

@@ -14,7 +14,7 @@
 namespace rgb200 {
 
 constexpr int PREPASS_THREADS = 256;
-constexpr int KMAJOR_CACHE_CHUNKS = 16;   // float4 chunks a thread keeps in registers
+constexpr int KMAJOR_MAX_CHUNKS = 16;     // most float4 chunks a thread keeps in registers
 
 __device__ __forceinline__ float abs4max(float m, float4 v) {
     return fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
@@ -36,55 +36,59 @@ __device__ __forceinline__ void store_quad(float4 v, const QuantScale& q, int8_t
     }
 }
 
-// Max over the TPR threads that share a row.  TPR == 32: one warp per row.  TPR == 256: one CTA per row.
+// Max over the TPR threads that share a row (TPR = 32, 64, 128 or 256; a CTA holds 256 / TPR rows).
+// Every thread of the CTA must call it when TPR > 32 (it contains a CTA-wide barrier).
 template <int TPR>
 __device__ __forceinline__ float row_group_max(float m, float* red) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
     if (TPR > 32) {
-        int w = threadIdx.x >> 5;
+        constexpr int WPG = TPR / 32;                  // warps per row group
+        const int w = threadIdx.x >> 5;
         if ((threadIdx.x & 31) == 0) red[w] = m;
         __syncthreads();
-        m = red[0];
+        const int g0 = (w / WPG) * WPG;
+        m = red[g0];
 #pragma unroll
-        for (int i = 1; i < TPR / 32; ++i) m = fmaxf(m, red[i]);
+        for (int i = 1; i < WPG; ++i) m = fmaxf(m, red[g0 + i]);
     }
     return m;
 }
 
 // ---------------------------------------------------------------------------------------------
 // k-contiguous operand: element (r, k) at src[r*K + k]   (A without trans_a, B with trans_b).
-// One read of the operand: a row group keeps its row in registers between the max and the split
-// (VEC path, K % 4 == 0, K <= 64 * TPR); otherwise the row is read again (it is still in L2).
+// One read of the operand: a group of TPR threads keeps its row in registers (CHUNKS float4 per
+// thread) between the max and the split.  VEC = false is the general path (any K, any alignment):
+// scalar loads, and the row is read a second time (it is still in L2).
 // grid = (ceil(R / (256 / TPR)), batch)
 // ---------------------------------------------------------------------------------------------
-template <int S, int TPR, bool VEC>
+template <int S, int TPR, int CHUNKS, bool VEC>
 __global__ void __launch_bounds__(PREPASS_THREADS)
 split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ given_max,
                     int8_t* __restrict__ planes, int* __restrict__ expo,
                     int R, int K, int Kp, long long src_batch_stride) {
     __shared__ float red[PREPASS_THREADS / 32];
-    const int rows_per_cta = PREPASS_THREADS / TPR;
+    constexpr int rows_per_cta = PREPASS_THREADS / TPR;
     const int row = blockIdx.x * rows_per_cta + threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
     const int b = blockIdx.y;
-    const bool live = row < R;                 // TPR == 256: uniform over the CTA; TPR == 32: over the warp
+    const bool live = row < R;
     const size_t plane_stride = (size_t)R * Kp;
     const float* a = src + (size_t)b * src_batch_stride + (size_t)(live ? row : 0) * K;
     int8_t* out = planes + (size_t)b * S * plane_stride + (size_t)(live ? row : 0) * Kp;
-    if (TPR == 32 && !live) return;            // whole warp leaves together; no CTA-wide barrier on this path
 
     float m = 0.0f;
     if (VEC) {
         const float4* a4 = reinterpret_cast<const float4*>(a);
         const int nq = K >> 2, nqp = Kp >> 2;
-        float4 v[KMAJOR_CACHE_CHUNKS];
+        float4 v[CHUNKS];
 #pragma unroll
-        for (int i = 0; i < KMAJOR_CACHE_CHUNKS; ++i) {
+        for (int i = 0; i < CHUNKS; ++i) {
             int c = t + i * TPR;
             v[i] = (live && c < nq) ? __ldg(a4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-            m = abs4max(m, v[i]);
         }
+#pragma unroll
+        for (int i = 0; i < CHUNKS; ++i) m = abs4max(m, v[i]);
         m = row_group_max<TPR>(m, red);
         if (!live) return;
         if (given_max) m = given_max[(size_t)b * R + row];
@@ -92,7 +96,7 @@ split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ giv
         if (t == 0) expo[(size_t)b * R + row] = e;
         const QuantScale q = quant_scale(e, S);
 #pragma unroll
-        for (int i = 0; i < KMAJOR_CACHE_CHUNKS; ++i) {
+        for (int i = 0; i < CHUNKS; ++i) {
             int c = t + i * TPR;
             if (c < nqp) store_quad<S>(v[i], q, out, plane_stride, (size_t)c * 4);   // c >= nq: zeros (k padding)
         }
@@ -137,12 +141,25 @@ colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ max
     float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
     const bool vec = (R & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) & 15) == 0);
     if (vec) {
-        if (r0 < R)
-            for (int k = k_lo + ty; k < k_hi; k += 8) {
-                float4 v = __ldg(reinterpret_cast<const float4*>(s + (size_t)k * R + r0));
+        if (r0 < R) {
+            const float4* p = reinterpret_cast<const float4*>(s + (size_t)(k_lo + ty) * R + r0);
+            const size_t step = (size_t)2 * R;       // 8 k-rows ahead, in float4 units (R % 4 == 0)
+            const int n = (k_hi - k_lo - ty + 7) / 8;
+            int i = 0;
+            for (; i + 4 <= n; i += 4) {             // four independent 16-byte loads in flight per thread
+                float4 v0 = __ldg(p), v1 = __ldg(p + step), v2 = __ldg(p + 2 * step), v3 = __ldg(p + 3 * step);
+                p += 4 * step;
+                m0 = fmaxf(fmaxf(m0, fmaxf(fabsf(v0.x), fabsf(v1.x))), fmaxf(fabsf(v2.x), fabsf(v3.x)));
+                m1 = fmaxf(fmaxf(m1, fmaxf(fabsf(v0.y), fabsf(v1.y))), fmaxf(fabsf(v2.y), fabsf(v3.y)));
+                m2 = fmaxf(fmaxf(m2, fmaxf(fabsf(v0.z), fabsf(v1.z))), fmaxf(fabsf(v2.z), fabsf(v3.z)));
+                m3 = fmaxf(fmaxf(m3, fmaxf(fabsf(v0.w), fabsf(v1.w))), fmaxf(fabsf(v2.w), fabsf(v3.w)));
+            }
+            for (; i < n; ++i, p += step) {
+                float4 v = __ldg(p);
                 m0 = fmaxf(m0, fabsf(v.x)); m1 = fmaxf(m1, fabsf(v.y));
                 m2 = fmaxf(m2, fabsf(v.z)); m3 = fmaxf(m3, fabsf(v.w));
             }
+        }
     } else {
         for (int k = k_lo + ty; k < k_hi; k += 8) {
             const float* p = s + (size_t)k * R + r0;
@@ -177,15 +194,17 @@ rowmax_kmajor_kernel(const float* __restrict__ src, float* __restrict__ out, int
     if ((threadIdx.x & 31) == 0) out[row] = m;
 }
 
-// Pass 2 for the k-strided operand: a 32 (r) x 128 (k) tile is read with r contiguous, transposed
-// through shared memory and written with k contiguous, 128 bytes per row and plane.
+// Pass 2 for the k-strided operand: a 32 (r) x 128 (k) tile is read with r contiguous (16-byte loads
+// where R allows), transposed through shared memory and written with k contiguous, 128 bytes per
+// row and plane.  Shared layout: tile[r][k] with the 16-byte column index XOR-ed by (r / 4) % 8, which
+// makes both the transposing stores and the row reads bank-conflict free.
 // grid = (ceil(R / 32), Kp / 128, batch)
 template <int S>
 __global__ void __launch_bounds__(PREPASS_THREADS)
 split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict__ maxbits,
                       int8_t* __restrict__ planes, int* __restrict__ expo,
                       int R, int K, int Kp, long long src_batch_stride) {
-    __shared__ __align__(16) float tile[32][128 + 4];   // [r][k]
+    __shared__ __align__(16) float tile[32 * 128];
     __shared__ int e_sh[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.z;
@@ -193,6 +212,7 @@ split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict_
     const float* s = src + (size_t)b * src_batch_stride;
     const size_t plane_stride = (size_t)R * Kp;
     int8_t* out = planes + (size_t)b * S * plane_stride;
+    auto slot = [](int r, int k) { return r * 128 + ((((k >> 2) ^ ((r >> 2) & 7))) << 2) + (k & 3); };
 
     if (threadIdx.x < 32) {
         int r = r0 + threadIdx.x;
@@ -200,23 +220,36 @@ split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict_
         e_sh[threadIdx.x] = e;
         if (r < R && blockIdx.y == 0) expo[(size_t)b * R + r] = e;
     }
-    // load: warp w takes k = k0 + w, w + 8, ...; lanes run along r (one 128-byte row segment)
-    {
+    const bool vec = (R & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) & 15) == 0);
+    if (vec) {
+        // a warp covers 4 k-rows x 32 r per load: lane = (k sub-row, group of four r)
+        const int kk4 = lane >> 3, rq = lane & 7, r = r0 + rq * 4;
+#pragma unroll 4
+        for (int kk = warp * 4 + kk4; kk < 128; kk += 32) {
+            const int k = k0 + kk;
+            float4 v = (r < R && k < K) ? __ldg(reinterpret_cast<const float4*>(s + (size_t)k * R + r))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+            tile[slot(rq * 4 + 0, kk)] = v.x;
+            tile[slot(rq * 4 + 1, kk)] = v.y;
+            tile[slot(rq * 4 + 2, kk)] = v.z;
+            tile[slot(rq * 4 + 3, kk)] = v.w;
+        }
+    } else {
         const int r = r0 + lane;
 #pragma unroll 4
         for (int kk = warp; kk < 128; kk += 8) {
-            int k = k0 + kk;
-            tile[lane][kk] = (r < R && k < K) ? __ldg(s + (size_t)k * R + r) : 0.0f;
+            const int k = k0 + kk;
+            tile[slot(lane, kk)] = (r < R && k < K) ? __ldg(s + (size_t)k * R + r) : 0.0f;
         }
     }
     __syncthreads();
     // split: warp w takes rows w, w + 8, ...; lanes run along k in groups of four
 #pragma unroll
     for (int rr = warp; rr < 32; rr += 8) {
-        int r = r0 + rr;
+        const int r = r0 + rr;
         if (r >= R) continue;
         const QuantScale q = quant_scale(e_sh[rr], S);
-        float4 v = *reinterpret_cast<const float4*>(&tile[rr][lane * 4]);
+        const float4 v = *reinterpret_cast<const float4*>(&tile[slot(rr, lane * 4)]);
         store_quad<S>(v, q, out, plane_stride, (size_t)r * Kp + k0 + lane * 4);
     }
 }
