@@ -20,18 +20,38 @@ __device__ __forceinline__ float abs4max(float m, float4 v) {
     return fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
 }
 
+// Fixed-point value of x plus the digit bias, Y = X + 64 * (128^(S-2) + ... + 1), by float arithmetic:
+// clamp in float (RNE commutes with clamping to an integer), then add 1.5 * 2^23 so that the FP32
+// adder itself performs the round-to-nearest-even to an integer (|v| < 2^22), and read the integer
+// from the mantissa.  With the bias every lower digit becomes an unsigned 7-bit field of Y:
+//   d[S-1] + 64 = Y & 127,  d[S-2] + 64 = (Y >> 7) & 127,  ...,  d[0] = Y >> 7(S-1)  (arithmetic shift).
+template <int S>
+__device__ __forceinline__ int biased_fixed_point(float x, const QuantScale& q, float limf) {
+    float v = __fmul_rn(__fmul_rn(x, q.f1), q.f2);
+    v = fminf(fmaxf(v, -limf), limf);
+    constexpr int BIAS = S == 1 ? 0 : (S == 2 ? 64 : 64 * 129);
+    return __float_as_int(__fadd_rn(v, 12582912.0f)) - (0x4B400000 - BIAS);
+}
+
+// Bytes 0 of four words -> one word (three byte permutes).
+__device__ __forceinline__ uint32_t pack_low_bytes(int a, int b, int c, int d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+// Four packed 7-bit fields (value + 64 each) -> four packed signed bytes, without borrows between bytes.
+__device__ __forceinline__ uint32_t unbias_bytes(uint32_t w) {
+    return (((w & 0x7F7F7F7Fu) | 0x80808080u) - 0x40404040u) ^ 0x80808080u;
+}
+
 // Quantise four consecutive k values and store them as one 32-bit word per digit plane.
 template <int S>
 __device__ __forceinline__ void store_quad(float4 v, const QuantScale& q, int8_t* plane0, size_t plane_stride, size_t idx) {
-    int d[4][S];
-    split_digits<S>(fixed_point(v.x, q), d[0]);
-    split_digits<S>(fixed_point(v.y, q), d[1]);
-    split_digits<S>(fixed_point(v.z, q), d[2]);
-    split_digits<S>(fixed_point(v.w, q), d[3]);
+    const float limf = (float)q.lim;
+    int y0 = biased_fixed_point<S>(v.x, q, limf), y1 = biased_fixed_point<S>(v.y, q, limf);
+    int y2 = biased_fixed_point<S>(v.z, q, limf), y3 = biased_fixed_point<S>(v.w, q, limf);
 #pragma unroll
-    for (int p = 0; p < S; ++p) {
-        uint32_t w = (uint32_t)(d[0][p] & 0xFF) | ((uint32_t)(d[1][p] & 0xFF) << 8) |
-                     ((uint32_t)(d[2][p] & 0xFF) << 16) | ((uint32_t)(d[3][p] & 0xFF) << 24);
+    for (int p = S - 1; p >= 0; --p) {
+        uint32_t w = pack_low_bytes(y0, y1, y2, y3);
+        if (p > 0) { w = unbias_bytes(w); y0 >>= 7; y1 >>= 7; y2 >>= 7; y3 >>= 7; }
         *reinterpret_cast<uint32_t*>(plane0 + p * plane_stride + idx) = w;
     }
 }

@@ -1,7 +1,7 @@
 // Source-compatible replacement for the reference's repro_gemm_cuda/repro_gemm.cuh (lines 25-75):
-// the same namespace, types, defaults and signatures, implemented as thin inline calls into the
-// C ABI of librgb200.so (include/rgb200.h).  A program written against the reference header builds
-// against this one unchanged; instead of compiling the reference's repro_gemm.cu it links -lrgb200.
+// the same namespace, types, defaults and signatures.  librgb200.so defines these functions (thin
+// C++ wrappers over its C ABI, include/rgb200.h), so a program written against the reference header
+// or against this one links -lrgb200 instead of compiling the reference's repro_gemm.cu.
 #pragma once
 #include <cuda_runtime.h>
 #include <cstddef>
@@ -41,39 +41,17 @@ struct Plan {
     size_t workspace_bytes;  // size needed by repro_gemm_fp32_ws
 };
 
-namespace detail {
-inline rgb200_config to_c(const Config& c) {
-    rgb200_config r;
-    r.split_k = c.split_k; r.tile_m = c.tile_m; r.tile_n = c.tile_n; r.tile_k = c.tile_k;
-    r.algo = static_cast<int>(c.algo); r.slices = c.slices;
-    r.trans_a = c.trans_a ? 1 : 0; r.trans_b = c.trans_b ? 1 : 0;
-    return r;
-}
-}  // namespace detail
+// Defined in librgb200.so with exactly these C++ signatures, so a program compiled against the
+// reference's own header links against the library as well.
+cudaError_t make_plan(int M, int N, int K, Config cfg, Plan* plan);
 
-inline cudaError_t make_plan(int M, int N, int K, Config cfg, Plan* plan) {
-    if (!plan) return cudaErrorInvalidValue;
-    rgb200_config c = detail::to_c(cfg);
-    rgb200_plan p;
-    int rc = rgb200_make_plan(M, N, K, &c, &p);
-    if (rc == 0) { plan->algo = static_cast<Algo>(p.algo); plan->split_k = p.split_k; plan->workspace_bytes = p.workspace_bytes; }
-    return static_cast<cudaError_t>(rc);
-}
+cudaError_t repro_gemm_fp32_ws(const float* A, const float* B, float* C, int M, int N, int K, Config cfg,
+                               void* workspace, size_t workspace_bytes, cudaStream_t stream = nullptr,
+                               const cudaEvent_t* stage_events = nullptr);
 
-inline cudaError_t repro_gemm_fp32_ws(const float* A, const float* B, float* C, int M, int N, int K, Config cfg,
-                                      void* workspace, size_t workspace_bytes, cudaStream_t stream = nullptr,
-                                      const cudaEvent_t* stage_events = nullptr) {
-    rgb200_config c = detail::to_c(cfg);
-    return static_cast<cudaError_t>(rgb200_gemm_fp32_ws(A, B, C, M, N, K, &c, workspace, workspace_bytes, stream,
-                                                        reinterpret_cast<void* const*>(stage_events)));
-}
+cudaError_t repro_gemm_fp32(const float* A, const float* B, float* C, int M, int N, int K, Config cfg = Config(),
+                            cudaStream_t stream = nullptr);
 
-inline cudaError_t repro_gemm_fp32(const float* A, const float* B, float* C, int M, int N, int K, Config cfg = Config(),
-                                   cudaStream_t stream = nullptr) {
-    rgb200_config c = detail::to_c(cfg);
-    return static_cast<cudaError_t>(rgb200_gemm_fp32(A, B, C, M, N, K, &c, stream));
-}
-
-inline const char* algo_name(Algo a) { return rgb200_algo_name(static_cast<int>(a)); }
+const char* algo_name(Algo a);
 
 }  // namespace repro_gemm

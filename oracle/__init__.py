@@ -14,6 +14,9 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "liboracle.so")
 _REF = os.path.join(_HERE, "_ref", "librepro_ref.so")
+_REF_CUDA = os.path.join(_HERE, "_ref", "librepro_ref_cuda.so")
+REF_TEST_TOOL = os.path.join(_HERE, "_ref", "test_repro_gemm_rgb200")
+REF_HASH_TOOL = os.path.join(_HERE, "_ref", "hash_repro_gemm_rgb200")
 
 FNV_OFFSET = 0xCBF29CE484222325
 
@@ -24,6 +27,8 @@ def build(force=False):
         subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True, capture_output=True)
     if force or not os.path.exists(_REF):
         subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+    if force or not os.path.exists(_REF_CUDA):
+        subprocess.run(["make", "-C", _HERE, "ref_gpu"], check=True, capture_output=True)
 
 
 def _f32(a):
@@ -84,6 +89,41 @@ def ref():
         R.ref_round_to_float.restype = C.c_float
         _ref = R
     return _ref
+
+
+_ref_cuda = None
+
+
+def ref_cuda():
+    """The reference's own CUDA kernels recompiled for sm_100a, or None where not built."""
+    global _ref_cuda
+    if _ref_cuda is None and os.path.exists(_REF_CUDA):
+        R = C.CDLL(_REF_CUDA)
+        vp, i = C.c_void_p, C.c_int
+        R.refcuda_plan.argtypes = [i] * 8 + [C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
+        R.refcuda_gemm_ws.argtypes = [vp, vp, vp] + [i] * 8 + [vp, C.c_size_t, vp, C.POINTER(vp)]
+        _ref_cuda = R
+    return _ref_cuda
+
+
+def ref_cuda_gemm(A, B, M, N, K, ta=False, tb=False, S=3, split_k=1, algo=0, events=None):
+    """Runs the reference's repro_gemm_fp32_ws on CUDA tensors A, B (torch); returns C [M, N]."""
+    import torch
+    R = ref_cuda()
+    eff, nbytes = C.c_int(0), C.c_size_t(0)
+    rc = R.refcuda_plan(M, N, K, split_k, algo, S, int(ta), int(tb), C.byref(eff), C.byref(nbytes))
+    if rc != 0:
+        raise RuntimeError("reference make_plan: cudaError %d" % rc)
+    ws = torch.empty(nbytes.value, dtype=torch.uint8, device=A.device)
+    out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    ev = None
+    if events is not None:
+        ev = (C.c_void_p * 4)(*[C.c_void_p(e.cuda_event) for e in events])
+    rc = R.refcuda_gemm_ws(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, split_k, algo, S, int(ta), int(tb),
+                           ws.data_ptr(), nbytes.value, torch.cuda.current_stream().cuda_stream, ev)
+    if rc != 0:
+        raise RuntimeError("reference repro_gemm_fp32_ws: cudaError %d" % rc)
+    return out
 
 
 def default_threads():
