@@ -44,6 +44,7 @@ def lib():
     L.rgb200_gemm_fp32.argtypes = [fp, fp, fp, i, i, i, cfgp, vp]
     L.rgb200_gemm_fp32_batched_ws.argtypes = [fp, fp, fp, i, i, i, i, ll, ll, ll, cfgp, vp, C.c_size_t, vp,
                                               C.POINTER(vp)]
+    L.rgb200_gemm_fp32_static.argtypes = [fp, fp, fp, i, i, i, cfgp, vp]
     L.rgb200_absmax.argtypes = [fp, i, i, i, fp, vp]
     L.rgb200_gemm_partial_ws.argtypes = [fp, fp, fp, fp, vp, i, i, i, ll, cfgp, vp, C.c_size_t, vp]
     L.rgb200_round_partial.argtypes = [vp, i, fp, fp, fp, i, i, i, vp]

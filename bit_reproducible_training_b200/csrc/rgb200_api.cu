@@ -308,7 +308,48 @@ cudaError_t gemm_ws(const float* A, const float* B, float* C, int M, int N, int 
 
 using namespace rgb200;
 
+// Fixed workspace of rgb200_gemm_fp32_static.  In host code this name is only a stand-in for the
+// device object: the address a kernel can use comes from cudaGetSymbolAddress, looked up once per
+// device with that device current (static_workspace_address below).
+static __device__ __align__(256) unsigned char rgb200_static_scratch[RGB200_STATIC_WORKSPACE_BYTES];
+
+namespace {
+void* g_static_ptr[MAX_DEVICES];
+cudaError_t g_static_err[MAX_DEVICES];
+std::once_flag g_static_once[MAX_DEVICES];
+
+cudaError_t static_workspace_address(void** out) {
+    int dev;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::call_once(g_static_once[dev], [dev] {
+        void* p = nullptr;
+        g_static_err[dev] = cudaGetSymbolAddress(&p, rgb200_static_scratch);   // the current device's copy
+        g_static_ptr[dev] = p;
+    });
+    if (g_static_err[dev] != cudaSuccess) return g_static_err[dev];
+    if (!g_static_ptr[dev]) return cudaErrorInvalidSymbol;
+    *out = g_static_ptr[dev];
+    return cudaSuccess;
+}
+}  // namespace
+
 extern "C" {
+
+int rgb200_gemm_fp32_static(const float* A, const float* B, float* C, int M, int N, int K, const rgb200_config* cfg,
+                            void* stream) {
+    rgb200_config def;
+    if (!cfg) { rgb200_default_config(&def); cfg = &def; }
+    if (!A || !B || !C) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = plan_layout(M, N, K, K, 1, *cfg, false, L);
+    if (e != cudaSuccess) return e;
+    if (L.total > (size_t)RGB200_STATIC_WORKSPACE_BYTES) return cudaErrorMemoryAllocation;   // does not fit the fixed array
+    void* ws = nullptr;
+    if ((e = static_workspace_address(&ws)) != cudaSuccess) return e;
+    return gemm_ws(A, B, C, M, N, K, 1, 0, 0, 0, cfg, ws, RGB200_STATIC_WORKSPACE_BYTES, stream, nullptr);
+}
 
 void rgb200_default_config(rgb200_config* cfg) {
     if (!cfg) return;

@@ -110,6 +110,20 @@ def repro_gemm_fp32(A, B, Cout, M, N, K, cfg=None, stream=None):
     return _lib.lib().rgb200_gemm_fp32(_ptr(A), _ptr(B), _ptr(Cout), M, N, K, C.byref(c), _stream(stream))
 
 
+STATIC_WORKSPACE_BYTES = 32 << 20
+cudaErrorMemoryAllocation = 2
+
+
+def repro_gemm_fp32_static(A, B, Cout, M, N, K, cfg=None, stream=None):
+    """Allocation-free run for callers that own no device memory besides A, B and C (for example
+    an operator living under a framework whose caching allocator must not be bypassed): the
+    workspace is a fixed STATIC_WORKSPACE_BYTES array inside the library.  Asynchronous on `stream`.
+    Returns the cudaError_t number; 2 means the problem needs more workspace than the array holds.
+    Calls share the array, so calls that overlap on the GPU race; keep them on one stream."""
+    c = (cfg or Config()).c()
+    return _lib.lib().rgb200_gemm_fp32_static(_ptr(A), _ptr(B), _ptr(Cout), M, N, K, C.byref(c), _stream(stream))
+
+
 def repro_gemm_fp32_batched_ws(A, B, Cout, M, N, K, batch, stride_a, stride_b, stride_c, cfg, workspace, stream=None,
                                stage_events=None):
     c = cfg.c()

@@ -111,6 +111,33 @@ int rgb200_round_partial(const long long* T, int parts, const float* max_a, cons
  * cudaGetLastError (repro_gemm_cuda/repro_gemm.cu:527); this is the same channel for that one case. */
 int rgb200_workspace_status(const void* workspace, int* status);
 
+/* Allocation-free variant of rgb200_gemm_fp32 (it has no counterpart in the reference, whose
+ * convenience call repro_gemm_fp32 allocates and frees its workspace on every call).
+ *
+ * Who needs it: code that is handed device pointers for A, B and C but has no way to obtain device
+ * memory of its own - an operator running under a host framework whose caching allocator owns all
+ * device memory (a raw cudaMalloc next to it synchronises the device and takes memory the allocator
+ * believes it can still hand out), a step of a latency-critical loop that must not hit the implicit
+ * device-wide synchronisation of cudaMalloc / cudaFree, or a plug-in layer that only sees tensors.
+ * Such callers cannot use rgb200_gemm_fp32 (it allocates) and have nothing to pass as the workspace of
+ * rgb200_gemm_fp32_ws.
+ *
+ * This call takes the digit planes, exponents and partial sums from a fixed array of
+ * RGB200_STATIC_WORKSPACE_BYTES that is part of the library image: every GPU that loads the library
+ * holds that much memory until the process exits.  It calls no cudaMalloc, cudaFree or allocating
+ * library routine.  Same arithmetic, same bits as the other entry points; asynchronous on `stream`.
+ *   - 2 (cudaErrorMemoryAllocation) is returned, and nothing is launched, when the problem needs more
+ *     workspace than the fixed array holds (rgb200_layout reports the need; 32 MiB covers for example
+ *     2048 x 2048 x 1024 or 1024 x 3072 x 768 at S = 3).  Other errors are those of rgb200_gemm_fp32_ws.
+ *   - The first call on each device looks up the array's device address; make that first call outside
+ *     any stream capture.
+ *   - All calls share the one array.  The library re-zeroes the part that must start at zero on every
+ *     call, but two calls that overlap on the GPU (different streams, or different threads without
+ *     ordering) race on it: issue them on one stream, or order them with events. */
+#define RGB200_STATIC_WORKSPACE_BYTES (32u << 20)
+int rgb200_gemm_fp32_static(const float* A, const float* B, float* C, int M, int N, int K,
+                            const rgb200_config* cfg, void* stream);
+
 /* Host-side helpers matching repro_gemm_cuda/repro_test_util.h:20-24 (FNV-1a-64 over raw bytes) and
  * repro_gemm_cuda/repro_gemm_math.cuh:59,74,96 (the three scalar functions, computed by this
  * library's own host code so callers can cross-check them without a GPU). */
