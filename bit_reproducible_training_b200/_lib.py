@@ -28,7 +28,7 @@ def lib():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB
+    path = os.environ.get("RGB200_LIBRARY") or _build.LIB      # explicit path override, e.g. for a tuned build
     if not os.path.exists(path):
         raise RuntimeError("%s is missing: run `python -m bit_reproducible_training_b200.build` "
                            "(or __graft_entry__.build()) first; there is no CPU fallback" % path)

@@ -120,6 +120,30 @@ RGB_HD uint64_t shr_rne(uint64_t m, int s) {   // s in [1, 63]
     return q + ((rest > half || (rest == half && (q & 1))) ? 1 : 0);
 }
 
+// Correctly rounded (nearest-even) binary32 bit pattern of the exact value m * 2^E (m > 0) by integer
+// arithmetic only: subnormals, overflow to infinity, values that round to zero.
+RGB_HD uint32_t round_magnitude_exact(uint64_t m, int E) {
+    int p = top_bit64(m);
+    int e = p + E;
+    if (e > 127) return 0x7F800000u;
+    if (e >= -126) {
+        int s = p - 23;
+        uint64_t q = s <= 0 ? m << (-s) : shr_rne(m, s);
+        if (q == (1ull << 24)) { q >>= 1; ++e; }
+        if (e > 127) return 0x7F800000u;
+        return ((uint32_t)(e + 127) << 23) | ((uint32_t)q & 0x7FFFFFu);
+    }
+    int s = -(E + 149);
+    uint64_t q = s <= 0 ? m << (-s) : (s >= 64 ? 0ull : shr_rne(m, s));
+    return (uint32_t)q;     // q == 2^23 encodes the smallest normal number, as it should
+}
+
+#ifdef __CUDA_ARCH__
+// Out of line on the device: it is rare (subnormal or overflowing results only) and inlining it at
+// every output of the unrolled epilogue would multiply the code size.
+__device__ __noinline__ uint32_t round_magnitude_rare(uint64_t m, int E) { return round_magnitude_exact(m, E); }
+#endif
+
 // Correctly rounded (nearest-even) binary32 bit pattern of the exact value T * 2^E: subnormals,
 // overflow to infinity, +0 for T == 0, and -0 for a negative value that rounds to zero.
 RGB_HD uint32_t round_to_f32_bits(long long T, int E) {
@@ -129,25 +153,13 @@ RGB_HD uint32_t round_to_f32_bits(long long T, int E) {
 #ifdef __CUDA_ARCH__
     // Fast path: one hardware RNE conversion to 24 bits, then an exact exponent adjustment,
     // valid whenever the scaled result is a normal number.
-    {
-        uint32_t fb = f32_bits(__ull2float_rn(m));
-        int e = (int)(fb >> 23) - 127 + E;
-        if (e >= -126 && e <= 127) return sign | (fb + ((uint32_t)E << 23));
-    }
+    uint32_t fb = f32_bits(__ull2float_rn(m));
+    int e = (int)(fb >> 23) - 127 + E;
+    if (e >= -126 && e <= 127) return sign | (fb + ((uint32_t)E << 23));
+    return sign | round_magnitude_rare(m, E);
+#else
+    return sign | round_magnitude_exact(m, E);
 #endif
-    int p = top_bit64(m);
-    int e = p + E;
-    if (e > 127) return sign | 0x7F800000u;
-    if (e >= -126) {
-        int s = p - 23;
-        uint64_t q = s <= 0 ? m << (-s) : shr_rne(m, s);
-        if (q == (1ull << 24)) { q >>= 1; ++e; }
-        if (e > 127) return sign | 0x7F800000u;
-        return sign | ((uint32_t)(e + 127) << 23) | ((uint32_t)q & 0x7FFFFFu);
-    }
-    int s = -(E + 149);
-    uint64_t q = s <= 0 ? m << (-s) : (s >= 64 ? 0ull : shr_rne(m, s));
-    return sign | (uint32_t)q;
 }
 
 }  // namespace rgb200

@@ -28,6 +28,14 @@
 #include <cuda.h>
 #include "rgb200_math.cuh"
 
+// Tunables (overridable at build time for experiments)
+#ifndef RGB200_L2_PREFETCH_DISTANCE
+#define RGB200_L2_PREFETCH_DISTANCE -1
+#endif
+#ifndef RGB200_TILE_GROUP_M
+#define RGB200_TILE_GROUP_M 8
+#endif
+
 namespace rgb200 {
 
 constexpr int BLOCK_M = 128;
@@ -61,7 +69,8 @@ struct GemmTraits {
     static constexpr int TMEM_COLS_USED = LEVELS * NT;
     static constexpr int TMEM_COLS = TMEM_COLS_USED <= 32 ? 32 : TMEM_COLS_USED <= 64 ? 64 :
                                      TMEM_COLS_USED <= 128 ? 128 : TMEM_COLS_USED <= 256 ? 256 : 512;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ +
+                                      EPI_WARPS * 32 * 4 /* column exponents, one slot per epilogue warp */;
     static_assert(TMEM_COLS_USED <= 512, "level accumulators do not fit TMEM");
     static_assert(S * NT <= 256 && (S * NT) % 16 == 0 && NT % 16 == 0, "invalid UMMA N");
     static_assert(STAGES >= 2, "pipeline needs two stages");
@@ -130,6 +139,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
+// Asks the TMA unit to bring a box into L2 only (no shared memory, no barrier): hides the DRAM
+// latency of operand panels that are touched for the first time.
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -187,7 +203,7 @@ __host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
 struct TileCoord { int batch, z, m_blk, n_blk, kb_begin, kb_end; };
 
 __device__ __forceinline__ TileCoord tile_coord(const GemmParams& P, long long tile) {
-    const int GROUP = 16;
+    const int GROUP = RGB200_TILE_GROUP_M;
     long long per_mat = (long long)P.m_tiles * P.n_tiles;
     long long bz = tile / per_mat;
     int t = (int)(tile - bz * per_mat);
@@ -203,6 +219,23 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& P, long long t
     c.kb_end = (int)((long long)P.k_blocks * (c.z + 1) / P.split);
     return c;
 }
+
+// Position in the flattened (tile, k block) sequence a CTA works through.
+struct KCursor { long long tile; TileCoord tc; int kb; bool valid; };
+
+__device__ __forceinline__ void cursor_start(KCursor& c, const GemmParams& P, long long first, long long total) {
+    c.tile = first;
+    c.valid = first < total;
+    if (c.valid) { c.tc = tile_coord(P, first); c.kb = c.tc.kb_begin; }
+}
+__device__ __forceinline__ void cursor_next(KCursor& c, const GemmParams& P, long long stride, long long total) {
+    if (++c.kb < c.tc.kb_end) return;
+    c.tile += stride;
+    c.valid = c.tile < total;
+    if (c.valid) { c.tc = tile_coord(P, c.tile); c.kb = c.tc.kb_begin; }
+}
+
+constexpr int L2_PREFETCH_DISTANCE = RGB200_L2_PREFETCH_DISTANCE;   // k blocks the L2 prefetch runs ahead of the shared-memory loads (< 0: off)
 
 template <int S, int NT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -222,6 +255,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + STAGES * Tr::STAGE_BYTES + 8 * (2 * STAGES + 2));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + STAGES * Tr::STAGE_BYTES + 8 * (2 * STAGES + 3));
+    int* eb_slots = reinterpret_cast<int*>(gen_base + STAGES * Tr::STAGE_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total_tiles = (long long)P.batch * P.split * P.m_tiles * P.n_tiles;
@@ -245,17 +279,26 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileCoord tc = tile_coord(P, tile);
-                for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1u;
-                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
-                    mbar_arrive_expect_tx(full_bar(s), Tr::STAGE_BYTES);
-                    const uint32_t sa = smem_base + s * Tr::STAGE_BYTES;
-                    tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, tc.m_blk * BLOCK_M, 0, tc.batch);
-                    tma_load_4d(sa + Tr::A_STAGE_BYTES, &tmap_b, full_bar(s), kb * BLOCK_K, tc.n_blk * NT, 0, tc.batch);
-                }
+            KCursor ld, pf;
+            cursor_start(ld, P, blockIdx.x, total_tiles);
+            cursor_start(pf, P, blockIdx.x, total_tiles);
+            auto prefetch = [&]() {
+                tma_prefetch_4d(&tmap_a, pf.kb * BLOCK_K, pf.tc.m_blk * BLOCK_M, 0, pf.tc.batch);
+                tma_prefetch_4d(&tmap_b, pf.kb * BLOCK_K, pf.tc.n_blk * NT, 0, pf.tc.batch);
+                cursor_next(pf, P, gridDim.x, total_tiles);
+            };
+            if (L2_PREFETCH_DISTANCE >= 0)
+                for (int i = 0; i < L2_PREFETCH_DISTANCE + STAGES && pf.valid; ++i) prefetch();
+            for (; ld.valid; ++it) {
+                if (L2_PREFETCH_DISTANCE >= 0 && pf.valid) prefetch();
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1u;
+                if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
+                mbar_arrive_expect_tx(full_bar(s), Tr::STAGE_BYTES);
+                const uint32_t sa = smem_base + s * Tr::STAGE_BYTES;
+                tma_load_4d(sa, &tmap_a, full_bar(s), ld.kb * BLOCK_K, ld.tc.m_blk * BLOCK_M, 0, ld.tc.batch);
+                tma_load_4d(sa + Tr::A_STAGE_BYTES, &tmap_b, full_bar(s), ld.kb * BLOCK_K, ld.tc.n_blk * NT, 0, ld.tc.batch);
+                cursor_next(ld, P, gridDim.x, total_tiles);
             }
             if (!ok) {
                 // abort: let copies that are still in flight land before the CTA gives up its shared memory
@@ -327,7 +370,15 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const int row = tc.m_blk * BLOCK_M + row_in_tile;
             const bool row_ok = row < P.M;
             const int ea = row_ok ? __ldg(P.expo_a + (size_t)tc.batch * P.M + row) : 0;
-            const int* eb = P.expo_b + (size_t)tc.batch * P.N;
+            const int col0 = tc.n_blk * NT + half * CPT;
+            // this warp's column exponents go through its own shared-memory slot: one coalesced load here,
+            // issued before the wait below, instead of a dependent global load per output in phase 2
+            int* eb_s = eb_slots + (warp - 2) * 32;
+            static_assert(CPT <= 32, "one exponent per lane");
+            __syncwarp();
+            if (!P.partial && lane < CPT)
+                eb_s[lane] = col0 + lane < P.N ? __ldg(P.expo_b + (size_t)tc.batch * P.N + col0 + lane) : 0;
+            __syncwarp();
             ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
@@ -353,7 +404,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             tc_fence_before();
             mbar_arrive(tmem_empty_bar);
             // phase 2: one rounding per output (or the raw sums), overlapped with the next tile's MMAs
-            const int col0 = tc.n_blk * NT + half * CPT;
             if (!row_ok || col0 >= P.N) continue;
             if (P.partial) {
                 long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col0;
@@ -373,16 +423,16 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
                     for (int j = 0; j < CPT; j += 4) {
                         uint4 o;
-                        o.x = round_to_f32_bits(T[j + 0], ebase + __ldg(eb + col0 + j + 0));
-                        o.y = round_to_f32_bits(T[j + 1], ebase + __ldg(eb + col0 + j + 1));
-                        o.z = round_to_f32_bits(T[j + 2], ebase + __ldg(eb + col0 + j + 2));
-                        o.w = round_to_f32_bits(T[j + 3], ebase + __ldg(eb + col0 + j + 3));
+                        o.x = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
+                        o.y = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
+                        o.z = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
+                        o.w = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
                         *reinterpret_cast<uint4*>(dst + j) = o;
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < CPT; ++j)
-                        if (col0 + j < P.N) dst[j] = bits_f32(round_to_f32_bits(T[j], ebase + __ldg(eb + col0 + j)));
+                        if (col0 + j < P.N) dst[j] = bits_f32(round_to_f32_bits(T[j], ebase + eb_s[j]));
                 }
             }
         }
