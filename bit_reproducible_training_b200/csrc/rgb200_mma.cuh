@@ -28,10 +28,9 @@
 #include <cuda.h>
 #include "rgb200_math.cuh"
 
-// Tunables (overridable at build time for experiments)
-#ifndef RGB200_L2_PREFETCH_DISTANCE
-#define RGB200_L2_PREFETCH_DISTANCE -1
-#endif
+// Build-time options.  RGB200_TILE_GROUP_M: row tiles per schedule group.  RGB200_TIMING_STAMPS (off by
+// default): CTA 0 writes clock64 stamps of its first five tiles (MMA start, MMA issued, epilogue sees the
+// accumulators, TMEM released) into the unused part of the workspace's status block, words 1..30.
 #ifndef RGB200_TILE_GROUP_M
 #define RGB200_TILE_GROUP_M 8
 #endif
@@ -139,13 +138,6 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
-// Asks the TMA unit to bring a box into L2 only (no shared memory, no barrier): hides the DRAM
-// latency of operand panels that are touched for the first time.
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -235,8 +227,6 @@ __device__ __forceinline__ void cursor_next(KCursor& c, const GemmParams& P, lon
     if (c.valid) { c.tc = tile_coord(P, c.tile); c.kb = c.tc.kb_begin; }
 }
 
-constexpr int L2_PREFETCH_DISTANCE = RGB200_L2_PREFETCH_DISTANCE;   // k blocks the L2 prefetch runs ahead of the shared-memory loads (< 0: off)
-
 template <int S, int NT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -279,23 +269,14 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            KCursor ld, pf;
+            KCursor ld;
             cursor_start(ld, P, blockIdx.x, total_tiles);
-            cursor_start(pf, P, blockIdx.x, total_tiles);
-            auto prefetch = [&]() {
-                tma_prefetch_4d(&tmap_a, pf.kb * BLOCK_K, pf.tc.m_blk * BLOCK_M, 0, pf.tc.batch);
-                tma_prefetch_4d(&tmap_b, pf.kb * BLOCK_K, pf.tc.n_blk * NT, 0, pf.tc.batch);
-                cursor_next(pf, P, gridDim.x, total_tiles);
-            };
-            if (L2_PREFETCH_DISTANCE >= 0)
-                for (int i = 0; i < L2_PREFETCH_DISTANCE + STAGES && pf.valid; ++i) prefetch();
             for (; ld.valid; ++it) {
-                if (L2_PREFETCH_DISTANCE >= 0 && pf.valid) prefetch();
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1u;
                 if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
-                mbar_arrive_expect_tx(full_bar(s), Tr::STAGE_BYTES);
                 const uint32_t sa = smem_base + s * Tr::STAGE_BYTES;
+                mbar_arrive_expect_tx(full_bar(s), Tr::STAGE_BYTES);
                 tma_load_4d(sa, &tmap_a, full_bar(s), ld.kb * BLOCK_K, ld.tc.m_blk * BLOCK_M, 0, ld.tc.batch);
                 tma_load_4d(sa + Tr::A_STAGE_BYTES, &tmap_b, full_bar(s), ld.kb * BLOCK_K, ld.tc.n_blk * NT, 0, ld.tc.batch);
                 cursor_next(ld, P, gridDim.x, total_tiles);
@@ -323,6 +304,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const TileCoord tc = tile_coord(P, tile);
                 if (!(ok = mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
                 tc_fence_after();
+#ifdef RGB200_TIMING_STAMPS
+                if (blockIdx.x == 0 && tile_it < 5) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 0] = clock64();
+#endif
                 for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -354,6 +338,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     umma_commit(empty_bar(s));          // frees the stage once these MMAs have read it
                 }
                 if (ok) umma_commit(tmem_full_bar);     // accumulators complete
+#ifdef RGB200_TIMING_STAMPS
+                if (blockIdx.x == 0 && tile_it < 5) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 1] = clock64();
+#endif
             }
         }
     } else {
@@ -383,6 +370,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
+#ifdef RGB200_TIMING_STAMPS
+            if (blockIdx.x == 0 && tile_it < 5 && threadIdx.x == 64) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 2] = clock64();
+#endif
             // phase 1: accumulators -> exact INT64 sums in registers, then release TMEM
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * CPT;
             long long T[CPT];
@@ -403,6 +393,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             }
             tc_fence_before();
             mbar_arrive(tmem_empty_bar);
+#ifdef RGB200_TIMING_STAMPS
+            if (blockIdx.x == 0 && tile_it < 5 && threadIdx.x == 64) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 3] = clock64();
+#endif
             // phase 2: one rounding per output (or the raw sums), overlapped with the next tile's MMAs
             if (!row_ok || col0 >= P.N) continue;
             if (P.partial) {
