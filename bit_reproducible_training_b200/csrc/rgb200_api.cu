@@ -46,6 +46,24 @@ double max_fixed_point(int S) {
     return top + low;
 }
 
+// K-range count chosen when the caller leaves split_k at 1 and the output has too few tiles to occupy
+// the GPU (for example 1024 x 768 x 50257: 96 tiles on 148 SMs, each 393 k blocks long).  Picks the
+// count that minimises the number of sequential k blocks per SM; never changes the output bits.
+constexpr int PLAN_SM_COUNT = 148;       // B200; the plan must not depend on a device query
+int auto_split(int M, int N, int batch, int k_blocks) {
+    const long long tiles = (long long)batch * ceil_div(M, BLOCK_M) * ceil_div(N, TILE_N);
+    if (tiles >= PLAN_SM_COUNT || k_blocks < 16) return 1;
+    if ((double)M * N * batch * sizeof(long long) > 32.0 * 1024 * 1024) return 1;   // keep the partial buffers small
+    int best = 1;
+    double best_cost = (double)ceil_div((int)tiles, PLAN_SM_COUNT) * k_blocks;
+    for (int s = 2; s <= 16 && s * 8 <= k_blocks; ++s) {
+        // per-SM sequential work in k blocks, plus a charge for the extra reduction kernel and its INT64 traffic
+        double cost = (double)((tiles * s + PLAN_SM_COUNT - 1) / PLAN_SM_COUNT) * ceil_div(k_blocks, s) + 8.0 + s;
+        if (cost < best_cost * 0.9) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
 cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const rgb200_config& cfg,
                         bool partial_out, Layout& L) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || cfg.split_k <= 0 || total_k < K) return cudaErrorInvalidValue;
@@ -65,7 +83,9 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
     if (L.algo == RGB200_ALGO_REFERENCE) {
         L.split = 1;            // the INT64 verification kernel never needs K ranges
     } else {
-        L.split = cfg.split_k > L.min_split ? cfg.split_k : L.min_split;
+        int want = cfg.split_k;
+        if (want == 1 && !partial_out) want = auto_split(M, N, batch, L.k_blocks);
+        L.split = want > L.min_split ? want : L.min_split;
         if (L.split > L.k_blocks) L.split = L.k_blocks;
     }
     L.partial_out = partial_out;

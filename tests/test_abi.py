@@ -82,9 +82,15 @@ def test_split_is_clamped_and_raised(L):
     assert rc == 0 and info.split_k == 7 and info.partial_bytes >= 7 * 128 * 128 * 8
     # one INT32 pass holds 105516 values of k at S = 3 (824 blocks of 128): longer K is cut automatically
     rc, info = layout(L, 128, 128, 824 * 128, slices=3)
-    assert rc == 0 and info.min_split == 1 and info.split_k == 1 and info.partial_bytes == 0
+    assert rc == 0 and info.min_split == 1
     rc, info = layout(L, 128, 128, 824 * 128 + 1, slices=3)
-    assert rc == 0 and info.min_split == 2 and info.split_k == 2
+    assert rc == 0 and info.min_split == 2 and info.split_k >= 2
+    # enough tiles to fill the GPU: no K ranges unless asked for or forced
+    rc, info = layout(L, 4096, 4096, 4096)
+    assert rc == 0 and info.split_k == 1 and info.partial_bytes == 0
+    # few tiles and a long K: the planner cuts K by itself
+    rc, info = layout(L, 1024, 768, 50257)
+    assert rc == 0 and info.split_k == 3 and info.partial_bytes >= 3 * 1024 * 768 * 8
     rc, info = layout(L, 128, 128, 1032 * 128 + 1, slices=2)
     assert rc == 0 and info.min_split == 2
     rc, info = layout(L, 128, 128, 1040 * 128 + 1, slices=1)

@@ -96,7 +96,7 @@ def test_long_k_is_cut_into_int32_safe_ranges():
     B = np.ones(K * N, dtype=np.float32)
     A[::7] = -1.0
     rc, plan = rg.make_plan(M, N, K, rg.Config())
-    assert rc == 0 and plan.split_k == 2
+    assert rc == 0 and plan.split_k >= 2
     got = rg.gemm(dev(A), dev(B), M, N, K).cpu().numpy()
     want = oracle.gemm(A, B, M, N, K)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
@@ -160,3 +160,65 @@ def test_repeated_runs_and_workspace_reuse_are_bit_stable():
     for _ in range(5):
         assert torch.equal(rg.gemm(A, B, n, n, n).view(torch.int32), first.view(torch.int32))
     assert not torch.equal(other, first)
+
+
+def test_auto_k_ranges_for_few_tiles():
+    """Few output tiles and a long K: the planner cuts K by itself (split_k left at 1) and the bits stay."""
+    M, N, K = 256, 192, 8192
+    rc, plan = rg.make_plan(M, N, K, rg.Config())
+    assert rc == 0 and plan.split_k > 1
+    A, B = fx.hash_tool_inputs("weights", M, N, K)
+    got = rg.gemm(dev(A), dev(B), M, N, K).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), oracle.gemm(A, B, M, N, K).view(np.uint32))
+
+
+def test_workspace_call_inside_a_cuda_graph():
+    """The allocation-free call is stream-ordered work only, so it can be captured once and replayed."""
+    n = 512
+    g = fx.Rng(5)
+    A, B = dev(g.normal(n * n)), dev(g.normal(n * n))
+    cfg = rg.Config()
+    rc, plan = rg.make_plan(n, n, n, cfg)
+    ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+    out = torch.zeros(n * n, device="cuda")
+    assert rg.repro_gemm_fp32_ws(A, B, out, n, n, n, cfg, ws) == 0          # first call: one-time set-up
+    torch.cuda.synchronize()
+    want = out.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        assert rg.repro_gemm_fp32_ws(A, B, out, n, n, n, cfg, ws) == 0
+    for _ in range(3):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int32), want.view(torch.int32))
+
+
+def test_linear_layer_forward_and_backward():
+    """Y = X W^T, dX = dY W, dW = dY^T X through autograd equal the oracle's three products."""
+    from bit_reproducible_training_b200 import layers
+    m, k, n = 96, 200, 72
+    g = fx.Rng(31)
+    X, W, dY = g.normal(m * k), g.normal(n * k, 0.02), g.normal(m * n, 1e-3)
+    lin = layers.Linear(k, n, bias=False).cuda()
+    with torch.no_grad():
+        lin.weight.copy_(dev(W).view(n, k))
+    x = dev(X).view(m, k).requires_grad_(True)
+    y = lin(x)
+    y.backward(dev(dY).view(m, n))
+    assert np.array_equal(y.detach().cpu().numpy().view(np.uint32), oracle.gemm(X, W, m, n, k, False, True).view(np.uint32))
+    assert np.array_equal(x.grad.cpu().numpy().view(np.uint32), oracle.gemm(dY, W, m, k, n).view(np.uint32))
+    assert np.array_equal(lin.weight.grad.cpu().numpy().view(np.uint32),
+                          oracle.gemm(dY, X, n, k, m, True, False).view(np.uint32))
+
+
+def test_suite_tool_writes_reference_format(tmp_path):
+    from bit_reproducible_training_b200 import suite
+    from test_oracle import SUITE_HASHES
+    path = tmp_path / "gpu.txt"
+    lines = suite.run(tokens=1024, reps=1, out=str(path))
+    assert lines[0].startswith("# GPU")
+    ops = [l.split("\t") for l in lines[1:]]
+    assert len(ops) == 21
+    for f in ops:
+        assert f[0] == "OP" and (f[3][3:], f[4][4:]) == SUITE_HASHES[f[1]]
