@@ -123,6 +123,7 @@ RGB_HD uint64_t shr_rne(uint64_t m, int s) {   // s in [1, 63]
 // Correctly rounded (nearest-even) binary32 bit pattern of the exact value m * 2^E (m > 0) by integer
 // arithmetic only: subnormals, overflow to infinity, values that round to zero.
 RGB_HD uint32_t round_magnitude_exact(uint64_t m, int E) {
+    if (m == 0) return 0u;
     int p = top_bit64(m);
     int e = p + E;
     if (e > 127) return 0x7F800000u;
@@ -161,5 +162,21 @@ RGB_HD uint32_t round_to_f32_bits(long long T, int E) {
     return sign | round_magnitude_exact(m, E);
 #endif
 }
+
+#ifdef __CUDA_ARCH__
+// Branch-free common case of round_to_f32_bits for unrolled epilogues: returns the result that is
+// valid when *ok stays true (the scaled value is a non-zero normal number); the caller redoes the
+// few outputs with ok == false through round_to_f32_bits.  Keeping branches out of the per-output
+// code lets the compiler interleave the independent outputs of a thread.
+__device__ __forceinline__ uint32_t round_to_f32_bits_fast(long long T, int E, bool* ok) {
+    const uint32_t sign = (uint32_t)((unsigned long long)T >> 32) & 0x80000000u;
+    const uint64_t m = (uint64_t)(T < 0 ? -T : T);
+    const uint32_t fb = f32_bits(__ull2float_rn(m));
+    const int e = (int)(fb >> 23) + E;                       // biased exponent of the scaled result
+    *ok = (unsigned)(e - 1) <= 253u;                         // 1..254: normal (m == 0 gives e = E, handled: see below)
+    if (m == 0) *ok = false;
+    return sign | (fb + ((uint32_t)E << 23));
+}
+#endif
 
 }  // namespace rgb200

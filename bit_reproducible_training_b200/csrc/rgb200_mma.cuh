@@ -416,10 +416,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
                     for (int j = 0; j < CPT; j += 4) {
                         uint4 o;
-                        o.x = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
-                        o.y = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
-                        o.z = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
-                        o.w = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
+                        bool k0, k1, k2, k3;
+                        o.x = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
+                        o.y = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
+                        o.z = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
+                        o.w = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                        if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
+                            o.x = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
+                            o.y = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
+                            o.z = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
+                            o.w = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
+                        }
                         *reinterpret_cast<uint4*>(dst + j) = o;
                     }
                 } else {
