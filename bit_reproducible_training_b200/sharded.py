@@ -8,8 +8,9 @@ work can be cut in two ways without changing one output bit:
   T[i, j] are formed entirely on one rank, so there is no collective on the data path.
 * K ranges: every rank owns a K range of both operands.  Ranks first agree on the row and column
   maxima (an element-wise max, exact and order-free), then form exact INT64 partial sums with the
-  shared scales, add them with an integer all-reduce (associative, cannot overflow: |T| <= 2^62 is
-  enforced for the whole K) and round once.
+  shared scales, add them with an integer reduction (associative, cannot overflow: |T| <= 2^62 is
+  enforced for the whole K) and round once.  Over NCCL the reduction is a reduce-scatter by row
+  blocks, each rank rounds its block, and an FP32 all-gather distributes C.
 
 The arithmetic backend is a parameter so the sharding logic can be exercised on CPU ranks (gloo)
 by the tests; the default backend is the CUDA library.
@@ -74,6 +75,18 @@ def gemm_k_sharded(A_k, B_k, M, N, k_local, total_k, cfg, group=None, backend=No
     dist.all_reduce(max_a, op=dist.ReduceOp.MAX, group=group)
     dist.all_reduce(max_b, op=dist.ReduceOp.MAX, group=group)
     T = backend.gemm_partial(A_k, B_k, max_a, max_b, M, N, k_local, total_k, cfg)
+    world = dist.get_world_size(group)
+    if world > 1 and M % world == 0 and dist.get_backend(group) == "nccl":
+        # reduce-scatter the INT64 sums by row blocks, round only the own block, all-gather FP32:
+        # 12 instead of 16 bytes per output cross the links and the rounding is shared between ranks
+        rank = dist.get_rank(group)
+        rows = M // world
+        T_own = torch.empty((rows, N), dtype=torch.int64, device=T.device)
+        dist.reduce_scatter_tensor(T_own, T, op=dist.ReduceOp.SUM, group=group)
+        C_own = backend.round_partial(T_own, max_a[rank * rows:(rank + 1) * rows].contiguous(), max_b, rows, N, cfg.slices)
+        C = torch.empty((M, N), dtype=torch.float32, device=T.device)
+        dist.all_gather_into_tensor(C, C_own, group=group)
+        return C
     dist.all_reduce(T, op=dist.ReduceOp.SUM, group=group)
     return backend.round_partial(T, max_a, max_b, M, N, cfg.slices)
 
