@@ -25,13 +25,23 @@ __device__ __forceinline__ float abs4max(float m, float4 v) {
 // adder itself performs the round-to-nearest-even to an integer (|v| < 2^22), and read the integer
 // from the mantissa.  With the bias every lower digit becomes an unsigned 7-bit field of Y:
 //   d[S-1] + 64 = Y & 127,  d[S-2] + 64 = (Y >> 7) & 127,  ...,  d[0] = Y >> 7(S-1)  (arithmetic shift).
-template <int S>
+// PLAIN rows (scale exponent e > -113, all but rows of denormal-range magnitude) need neither the
+// second factor (2^n fits one float) nor the clamp (it can only trigger when max|x|/127 is subnormal
+// and loses relative precision), so they take three instructions per element.
+template <int S, bool PLAIN>
 __device__ __forceinline__ int biased_fixed_point(float x, const QuantScale& q, float limf) {
-    float v = __fmul_rn(__fmul_rn(x, q.f1), q.f2);
-    v = fminf(fmaxf(v, -limf), limf);
+    float v = __fmul_rn(x, q.f1);
+    if (!PLAIN) {
+        v = __fmul_rn(v, q.f2);
+        v = fminf(fmaxf(v, -limf), limf);
+    }
     constexpr int BIAS = S == 1 ? 0 : (S == 2 ? 64 : 64 * 129);
     return __float_as_int(__fadd_rn(v, 12582912.0f)) - (0x4B400000 - BIAS);
 }
+
+// True when the row can take the PLAIN path: the scaling is a single normal factor and the quotient
+// max|x| / 127 that defined e was a normal float (e >= -126 + 7 leaves a wide margin).
+__device__ __forceinline__ bool plain_row(int e) { return e > -113; }
 
 // Bytes 0 of four words -> one word (three byte permutes).
 __device__ __forceinline__ uint32_t pack_low_bytes(int a, int b, int c, int d) {
@@ -43,17 +53,22 @@ __device__ __forceinline__ uint32_t unbias_bytes(uint32_t w) {
 }
 
 // Quantise four consecutive k values and store them as one 32-bit word per digit plane.
-template <int S>
-__device__ __forceinline__ void store_quad(float4 v, const QuantScale& q, int8_t* plane0, size_t plane_stride, size_t idx) {
+template <int S, bool PLAIN>
+__device__ __forceinline__ void store_quad_impl(float4 v, const QuantScale& q, int8_t* plane0, size_t plane_stride, size_t idx) {
     const float limf = (float)q.lim;
-    int y0 = biased_fixed_point<S>(v.x, q, limf), y1 = biased_fixed_point<S>(v.y, q, limf);
-    int y2 = biased_fixed_point<S>(v.z, q, limf), y3 = biased_fixed_point<S>(v.w, q, limf);
+    int y0 = biased_fixed_point<S, PLAIN>(v.x, q, limf), y1 = biased_fixed_point<S, PLAIN>(v.y, q, limf);
+    int y2 = biased_fixed_point<S, PLAIN>(v.z, q, limf), y3 = biased_fixed_point<S, PLAIN>(v.w, q, limf);
 #pragma unroll
     for (int p = S - 1; p >= 0; --p) {
         uint32_t w = pack_low_bytes(y0, y1, y2, y3);
         if (p > 0) { w = unbias_bytes(w); y0 >>= 7; y1 >>= 7; y2 >>= 7; y3 >>= 7; }
         *reinterpret_cast<uint32_t*>(plane0 + p * plane_stride + idx) = w;
     }
+}
+template <int S>
+__device__ __forceinline__ void store_quad(float4 v, const QuantScale& q, bool plain, int8_t* plane0, size_t plane_stride, size_t idx) {
+    if (plain) store_quad_impl<S, true>(v, q, plane0, plane_stride, idx);
+    else store_quad_impl<S, false>(v, q, plane0, plane_stride, idx);
 }
 
 // Max over the TPR threads that share a row (TPR = 32, 64, 128 or 256; a CTA holds 256 / TPR rows).
@@ -115,10 +130,18 @@ split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ giv
         const int e = scale_exponent(m);
         if (t == 0) expo[(size_t)b * R + row] = e;
         const QuantScale q = quant_scale(e, S);
+        if (plain_row(e)) {                      // uniform over the row group
 #pragma unroll
-        for (int i = 0; i < CHUNKS; ++i) {
-            int c = t + i * TPR;
-            if (c < nqp) store_quad<S>(v[i], q, out, plane_stride, (size_t)c * 4);   // c >= nq: zeros (k padding)
+            for (int i = 0; i < CHUNKS; ++i) {
+                int c = t + i * TPR;
+                if (c < nqp) store_quad_impl<S, true>(v[i], q, out, plane_stride, (size_t)c * 4);   // c >= nq: zeros (k padding)
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) {
+                int c = t + i * TPR;
+                if (c < nqp) store_quad_impl<S, false>(v[i], q, out, plane_stride, (size_t)c * 4);
+            }
         }
     } else {
         if (live && !given_max)
@@ -135,7 +158,7 @@ split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ giv
             v.y = k + 1 < K ? __ldg(a + k + 1) : 0.f;
             v.z = k + 2 < K ? __ldg(a + k + 2) : 0.f;
             v.w = k + 3 < K ? __ldg(a + k + 3) : 0.f;
-            store_quad<S>(v, q, out, plane_stride, (size_t)k);
+            store_quad<S>(v, q, plain_row(e), out, plane_stride, (size_t)k);
         }
     }
 }
@@ -268,9 +291,10 @@ split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict_
     for (int rr = warp; rr < 32; rr += 8) {
         const int r = r0 + rr;
         if (r >= R) continue;
-        const QuantScale q = quant_scale(e_sh[rr], S);
+        const int e = e_sh[rr];
+        const QuantScale q = quant_scale(e, S);
         const float4 v = *reinterpret_cast<const float4*>(&tile[slot(rr, lane * 4)]);
-        store_quad<S>(v, q, out, plane_stride, (size_t)r * Kp + k0 + lane * 4);
+        store_quad<S>(v, q, plain_row(e), out, plane_stride, (size_t)r * Kp + k0 + lane * 4);   // uniform over the warp
     }
 }
 
