@@ -117,7 +117,11 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
 // ------------------------------------------------------------------------------------------
 // Per-device facts, looked up once (immutable afterwards)
 // ------------------------------------------------------------------------------------------
-struct DeviceInfo { int sm_count = 0; int cc = 0; bool attrs_set = false; cudaError_t err = cudaSuccess; };
+struct DeviceInfo {
+    int sm_count = 0; int cc = 0; bool attrs_set = false; cudaError_t err = cudaSuccess;
+    // side stream and events for running the two operands' pre-passes next to each other
+    cudaStream_t side = nullptr; cudaEvent_t fork_ev = nullptr, join_ev = nullptr; mutable std::mutex fork_mutex;
+};
 DeviceInfo g_dev[MAX_DEVICES];
 std::once_flag g_dev_once[MAX_DEVICES];
 
@@ -147,6 +151,12 @@ cudaError_t device_info(const DeviceInfo** out) {
             if ((e2 = set_kernel_attrs<1>()) != cudaSuccess || (e2 = set_kernel_attrs<2>()) != cudaSuccess ||
                 (e2 = set_kernel_attrs<3>()) != cudaSuccess) { d.err = e2; return; }
             d.attrs_set = true;
+            if (cudaStreamCreateWithFlags(&d.side, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&d.fork_ev, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&d.join_ev, cudaEventDisableTiming) != cudaSuccess) {
+                d.side = nullptr;             // the pre-passes then simply run one after the other
+                (void)cudaGetLastError();
+            }
         }
     });
     if (g_dev[dev].err != cudaSuccess) return g_dev[dev].err;
@@ -258,8 +268,25 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     cudaError_t e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
     if (e != cudaSuccess) return e;
     record(0);
-    launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, a.st);
+    // The two operands are independent until the MMA kernel.  For large operands A's split runs on a side
+    // stream next to B's (fork and join by events, so the caller's stream still orders everything; this
+    // also holds inside a stream capture).  cudaStreamWaitEvent binds to the record made just before it,
+    // and the mutex keeps another host thread from re-recording the shared event in between.
+    const bool fork = dev.side != nullptr && (double)L.batch * L.K * ((double)L.M + L.N) >= 8.0e6;
+    bool forked = false;
+    if (fork) {
+        std::lock_guard<std::mutex> lock(dev.fork_mutex);
+        forked = cudaEventRecord(dev.fork_ev, a.st) == cudaSuccess &&
+                 cudaStreamWaitEvent(dev.side, dev.fork_ev, 0) == cudaSuccess;
+        if (!forked) (void)cudaGetLastError();
+    }
+    launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, forked ? dev.side : a.st);
     launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, a.st);
+    if (forked) {
+        std::lock_guard<std::mutex> lock(dev.fork_mutex);
+        if (cudaEventRecord(dev.join_ev, dev.side) != cudaSuccess || cudaStreamWaitEvent(a.st, dev.join_ev, 0) != cudaSuccess)
+            return cudaErrorUnknown;          // the side stream could not be joined: do not run on half-ordered data
+    }
     record(1);
 
     if (L.algo == RGB200_ALGO_REFERENCE) {
