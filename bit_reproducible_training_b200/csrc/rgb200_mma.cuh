@@ -212,6 +212,30 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& P, long long t
     return c;
 }
 
+// Stores CPT consecutive values of one row whose start is HEAD elements before a 16-byte boundary:
+// HEAD scalar stores, then 16-byte stores, then the scalar rest.  Rows of C are 16-byte aligned only
+// when N % 4 == 0 (and the base pointer is); for ragged N the alignment changes from row to row.
+template <int CPT, int HEAD>
+__device__ __forceinline__ void store_row_u32(uint32_t* dst, const uint32_t (&o)[CPT]) {
+#pragma unroll
+    for (int j = 0; j < HEAD; ++j) dst[j] = o[j];
+    constexpr int BODY = (CPT - HEAD) / 4;
+#pragma unroll
+    for (int i = 0; i < BODY; ++i)
+        *reinterpret_cast<uint4*>(dst + HEAD + 4 * i) = make_uint4(o[HEAD + 4 * i], o[HEAD + 4 * i + 1], o[HEAD + 4 * i + 2], o[HEAD + 4 * i + 3]);
+#pragma unroll
+    for (int j = HEAD + 4 * BODY; j < CPT; ++j) dst[j] = o[j];
+}
+template <int CPT, int HEAD>
+__device__ __forceinline__ void store_row_i64(long long* dst, const long long (&t)[CPT]) {
+    if (HEAD) dst[0] = t[0];
+    constexpr int BODY = (CPT - HEAD) / 2;
+#pragma unroll
+    for (int i = 0; i < BODY; ++i)
+        *reinterpret_cast<longlong2*>(dst + HEAD + 2 * i) = make_longlong2(t[HEAD + 2 * i], t[HEAD + 2 * i + 1]);
+    if (HEAD) dst[CPT - 1] = t[CPT - 1];
+}
+
 // Position in the flattened (tile, k block) sequence a CTA works through.
 struct KCursor { long long tile; TileCoord tc; int kb; bool valid; };
 
@@ -400,39 +424,54 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             if (!row_ok || col0 >= P.N) continue;
             if (P.partial) {
                 long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col0;
-                const bool vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col0 + CPT <= P.N;
-                if (vec) {
-#pragma unroll
-                    for (int j = 0; j < CPT; j += 2) *reinterpret_cast<longlong2*>(dst + j) = make_longlong2(T[j], T[j + 1]);
+                if (col0 + CPT <= P.N) {
+                    if ((reinterpret_cast<uintptr_t>(dst) & 8) == 0) store_row_i64<CPT, 0>(dst, T);
+                    else store_row_i64<CPT, 1>(dst, T);
                 } else {
 #pragma unroll
                     for (int j = 0; j < CPT; ++j) if (col0 + j < P.N) dst[j] = T[j];
                 }
             } else {
-                float* dst = P.C + (size_t)tc.batch * P.stride_c + (size_t)row * P.N + col0;
+                uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)tc.batch * P.stride_c + (size_t)row * P.N + col0);
                 const int ebase = ea + P.e0;
-                const bool vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && col0 + CPT <= P.N;
-                if (vec) {
+                auto round4 = [&](int j, uint32_t (&r)[4]) {
+                    bool k0, k1, k2, k3;
+                    r[0] = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
+                    r[1] = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
+                    r[2] = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
+                    r[3] = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                    if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
+                        r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
+                        r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
+                        r[2] = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
+                        r[3] = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
+                    }
+                };
+                const int past = (int)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3);    // elements past a 16-byte boundary
+                if (past == 0 && col0 + CPT <= P.N) {
+                    // aligned row segment: round four, store sixteen bytes, so stores overlap the next roundings
 #pragma unroll
                     for (int j = 0; j < CPT; j += 4) {
-                        uint4 o;
-                        bool k0, k1, k2, k3;
-                        o.x = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
-                        o.y = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
-                        o.z = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
-                        o.w = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
-                        if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
-                            o.x = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
-                            o.y = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
-                            o.z = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
-                            o.w = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
-                        }
-                        *reinterpret_cast<uint4*>(dst + j) = o;
+                        uint32_t r[4];
+                        round4(j, r);
+                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
                     }
                 } else {
+                    uint32_t o[CPT];
 #pragma unroll
-                    for (int j = 0; j < CPT; ++j)
-                        if (col0 + j < P.N) dst[j] = bits_f32(round_to_f32_bits(T[j], ebase + eb_s[j]));
+                    for (int j = 0; j < CPT; j += 4) {
+                        uint32_t r[4];
+                        round4(j, r);
+                        o[j] = r[0]; o[j + 1] = r[1]; o[j + 2] = r[2]; o[j + 3] = r[3];
+                    }
+                    if (col0 + CPT <= P.N) {
+                        if (past == 1) store_row_u32<CPT, 3>(dst, o);
+                        else if (past == 2) store_row_u32<CPT, 2>(dst, o);
+                        else store_row_u32<CPT, 1>(dst, o);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j) if (col0 + j < P.N) dst[j] = o[j];
+                    }
                 }
             }
         }
