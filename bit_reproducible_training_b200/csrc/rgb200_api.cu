@@ -23,7 +23,15 @@ constexpr int MAX_DEVICES = 64;
 inline size_t align_up(size_t x) { return (x + ALIGN - 1) / ALIGN * ALIGN; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-constexpr int TILE_N = 64;   // columns of C per CTA tile (the MMA is S*TILE_N wide)
+// Columns of C per CTA tile (the MMA is S * tile wide).  TMEM holds (2S-1) * tile INT32 columns and the
+// epilogue keeps tile/2 exact sums per thread in registers, which bounds the tile at 64 (S=3), 96 (S=2)
+// and 256 (S=1); narrow outputs take the 64-wide tile so little of the MMA is spent on padding.
+constexpr int TILE_N_BASE = 64;
+inline int tile_n_for(int S, int N) {
+    if (S == 1 && N >= 512) return 256;
+    if (S == 2 && N >= 192) return 96;
+    return TILE_N_BASE;
+}
 
 // ------------------------------------------------------------------------------------------
 // Planning (pure host arithmetic)
@@ -50,8 +58,8 @@ double max_fixed_point(int S) {
 // the GPU (for example 1024 x 768 x 50257: 96 tiles on 148 SMs, each 393 k blocks long).  Picks the
 // count that minimises the number of sequential k blocks per SM; never changes the output bits.
 constexpr int PLAN_SM_COUNT = 148;       // B200; the plan must not depend on a device query
-int auto_split(int M, int N, int batch, int k_blocks) {
-    const long long tiles = (long long)batch * ceil_div(M, BLOCK_M) * ceil_div(N, TILE_N);
+int auto_split(int M, int N, int batch, int k_blocks, int tile_n) {
+    const long long tiles = (long long)batch * ceil_div(M, BLOCK_M) * ceil_div(N, tile_n);
     if (tiles >= PLAN_SM_COUNT || k_blocks < 16) return 1;
     if ((double)M * N * batch * sizeof(long long) > 32.0 * 1024 * 1024) return 1;   // keep the partial buffers small
     int best = 1;
@@ -73,6 +81,8 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
     const double d = max_fixed_point(S);
     if ((double)total_k * d * d > std::ldexp(1.0, 62)) return cudaErrorInvalidValue;   // INT64 must hold any sum
     if ((long long)K + BLOCK_K > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+    // launch-geometry limits: the batch index is a grid y/z coordinate, row counts times batch are 32-bit
+    if (batch > 65535 || (long long)batch * (M > N ? M : N) > 0x7FFFFFFFll) return cudaErrorInvalidValue;
 
     L.S = S; L.M = M; L.N = N; L.K = K; L.batch = batch;
     L.Kp = ceil_div(K, BLOCK_K) * BLOCK_K;
@@ -84,7 +94,7 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
         L.split = 1;            // the INT64 verification kernel never needs K ranges
     } else {
         int want = cfg.split_k;
-        if (want == 1 && !partial_out) want = auto_split(M, N, batch, L.k_blocks);
+        if (want == 1 && !partial_out) want = auto_split(M, N, batch, L.k_blocks, tile_n_for(S, N));
         L.split = want > L.min_split ? want : L.min_split;
         if (L.split > L.k_blocks) L.split = L.k_blocks;
     }
@@ -125,10 +135,10 @@ struct DeviceInfo {
 DeviceInfo g_dev[MAX_DEVICES];
 std::once_flag g_dev_once[MAX_DEVICES];
 
-template <int S>
+template <int S, int NT>
 cudaError_t set_kernel_attrs() {
-    return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<S, TILE_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                GemmTraits<S, TILE_N>::SMEM_BYTES);
+    return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<S, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                GemmTraits<S, NT>::SMEM_BYTES);
 }
 
 cudaError_t device_info(const DeviceInfo** out) {
@@ -148,8 +158,9 @@ cudaError_t device_info(const DeviceInfo** out) {
         }
         d.cc = major * 10 + minor;
         if (d.cc == 100) {   // the only architecture this library carries code for
-            if ((e2 = set_kernel_attrs<1>()) != cudaSuccess || (e2 = set_kernel_attrs<2>()) != cudaSuccess ||
-                (e2 = set_kernel_attrs<3>()) != cudaSuccess) { d.err = e2; return; }
+            if ((e2 = set_kernel_attrs<1, 64>()) != cudaSuccess || (e2 = set_kernel_attrs<2, 64>()) != cudaSuccess ||
+                (e2 = set_kernel_attrs<3, 64>()) != cudaSuccess || (e2 = set_kernel_attrs<1, 256>()) != cudaSuccess ||
+                (e2 = set_kernel_attrs<2, 96>()) != cudaSuccess) { d.err = e2; return; }
             d.attrs_set = true;
             if (cudaStreamCreateWithFlags(&d.side, cudaStreamNonBlocking) != cudaSuccess ||
                 cudaEventCreateWithFlags(&d.fork_ev, cudaEventDisableTiming) != cudaSuccess ||
@@ -253,7 +264,6 @@ struct RunArgs {
 
 template <int S>
 cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
-    using Tr = GemmTraits<S, TILE_N>;
     auto record = [&](int i) { if (a.ev) cudaEventRecord(a.ev[i], a.st); };
     int8_t* qa = reinterpret_cast<int8_t*>(a.ws + L.qa);
     int8_t* qb = reinterpret_cast<int8_t*>(a.ws + L.qb);
@@ -297,9 +307,10 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         return cudaGetLastError();
     }
 
+    const int tile_n = tile_n_for(S, L.N);
     CUtensorMap map_a, map_b;
     if ((e = encode_planes_map(&map_a, qa, L.M, L.Kp, S, L.batch, BLOCK_M)) != cudaSuccess) return e;
-    if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, TILE_N)) != cudaSuccess) return e;
+    if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, tile_n)) != cudaSuccess) return e;
     GemmParams P;
     P.expo_a = ea; P.expo_b = eb;
     P.C = part ? nullptr : a.C;
@@ -310,11 +321,16 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     P.k_blocks = L.k_blocks;
     P.split = L.split;
     P.m_tiles = ceil_div(L.M, BLOCK_M);
-    P.n_tiles = ceil_div(L.N, TILE_N);
+    P.n_tiles = ceil_div(L.N, tile_n);
     P.e0 = e0;
     const long long tiles = (long long)L.batch * L.split * P.m_tiles * P.n_tiles;
     const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
-    gemm_i8_tcgen05_kernel<S, TILE_N><<<grid, GEMM_THREADS, Tr::SMEM_BYTES, a.st>>>(map_a, map_b, P);
+    if (S == 1 && tile_n == 256)
+        gemm_i8_tcgen05_kernel<1, 256><<<grid, GEMM_THREADS, GemmTraits<1, 256>::SMEM_BYTES, a.st>>>(map_a, map_b, P);
+    else if (S == 2 && tile_n == 96)
+        gemm_i8_tcgen05_kernel<2, 96><<<grid, GEMM_THREADS, GemmTraits<2, 96>::SMEM_BYTES, a.st>>>(map_a, map_b, P);
+    else
+        gemm_i8_tcgen05_kernel<S, TILE_N_BASE><<<grid, GEMM_THREADS, GemmTraits<S, TILE_N_BASE>::SMEM_BYTES, a.st>>>(map_a, map_b, P);
     record(2);
     if (L.use_partial_ws) {
         const size_t total = (size_t)L.batch * L.M * L.N;
@@ -420,7 +436,7 @@ int rgb200_layout(int M, int N, int K, int batch, const rgb200_config* cfg, rgb2
     cudaError_t e = plan_layout(M, N, K, K, batch, *cfg, false, L);
     if (e != cudaSuccess) return e;
     info->k_padded = L.Kp; info->k_blocks = L.k_blocks; info->min_split = L.min_split; info->split_k = L.split;
-    info->tile_n = TILE_N;
+    info->tile_n = tile_n_for(L.S, N);
     info->planes_a = (size_t)batch * L.S * M * L.Kp; info->planes_b = (size_t)batch * L.S * N * L.Kp;
     info->partial_bytes = L.total - L.part;
     info->workspace_bytes = L.total;

@@ -26,6 +26,7 @@
 // exit, which frees the CTA's TMEM.
 #pragma once
 #include <cuda.h>
+#include <type_traits>
 #include "rgb200_math.cuh"
 
 // Build-time options.  RGB200_TILE_GROUP_M: row tiles per schedule group.  RGB200_TIMING_STAMPS (off by
@@ -69,7 +70,7 @@ struct GemmTraits {
     static constexpr int TMEM_COLS = TMEM_COLS_USED <= 32 ? 32 : TMEM_COLS_USED <= 64 ? 64 :
                                      TMEM_COLS_USED <= 128 ? 128 : TMEM_COLS_USED <= 256 ? 256 : 512;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ +
-                                      EPI_WARPS * 32 * 4 /* column exponents, one slot per epilogue warp */;
+                                      EPI_WARPS * (NT / 2) * 4 /* column exponents, one slot per epilogue warp */;
     static_assert(TMEM_COLS_USED <= 512, "level accumulators do not fit TMEM");
     static_assert(S * NT <= 256 && (S * NT) % 16 == 0 && NT % 16 == 0, "invalid UMMA N");
     static_assert(STAGES >= 2, "pipeline needs two stages");
@@ -226,13 +227,13 @@ __device__ __forceinline__ void store_row_u32(uint32_t* dst, const uint32_t (&o)
 #pragma unroll
     for (int j = HEAD + 4 * BODY; j < CPT; ++j) dst[j] = o[j];
 }
-template <int CPT, int HEAD>
-__device__ __forceinline__ void store_row_i64(long long* dst, const long long (&t)[CPT]) {
+template <int CPT, int HEAD, class TAcc>
+__device__ __forceinline__ void store_row_i64(long long* dst, const TAcc (&t)[CPT]) {
     if (HEAD) dst[0] = t[0];
     constexpr int BODY = (CPT - HEAD) / 2;
 #pragma unroll
     for (int i = 0; i < BODY; ++i)
-        *reinterpret_cast<longlong2*>(dst + HEAD + 2 * i) = make_longlong2(t[HEAD + 2 * i], t[HEAD + 2 * i + 1]);
+        *reinterpret_cast<longlong2*>(dst + HEAD + 2 * i) = make_longlong2((long long)t[HEAD + 2 * i], (long long)t[HEAD + 2 * i + 1]);
     if (HEAD) dst[CPT - 1] = t[CPT - 1];
 }
 
@@ -371,6 +372,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         constexpr int CPT = NT / 2;                    // columns per thread
         static_assert(CPT % 16 == 0, "epilogue reads TMEM sixteen columns at a time");
+        // exact sums kept in registers between the TMEM drain and the rounding: one level (S = 1) fits INT32
+        using TAcc = typename std::conditional<S == 1, int, long long>::type;
+        static_assert(CPT * (S == 1 ? 1 : 2) <= 128, "the tile's sums must fit the register file");
         const int quarter = warp & 3;                  // TMEM lanes this warp may read: 32*quarter .. +31
         const int half = (warp - 2) >> 2;              // which half of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
@@ -384,11 +388,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const int col0 = tc.n_blk * NT + half * CPT;
             // this warp's column exponents go through its own shared-memory slot: one coalesced load here,
             // issued before the wait below, instead of a dependent global load per output in phase 2
-            int* eb_s = eb_slots + (warp - 2) * 32;
-            static_assert(CPT <= 32, "one exponent per lane");
+            int* eb_s = eb_slots + (warp - 2) * CPT;
             __syncwarp();
-            if (!P.partial && lane < CPT)
-                eb_s[lane] = col0 + lane < P.N ? __ldg(P.expo_b + (size_t)tc.batch * P.N + col0 + lane) : 0;
+            if (!P.partial)
+                for (int c = lane; c < CPT; c += 32)
+                    eb_s[c] = col0 + c < P.N ? __ldg(P.expo_b + (size_t)tc.batch * P.N + col0 + c) : 0;
             __syncwarp();
             ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
@@ -399,7 +403,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #endif
             // phase 1: accumulators -> exact INT64 sums in registers, then release TMEM
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * CPT;
-            long long T[CPT];
+            TAcc T[CPT];
 #pragma unroll
             for (int c0 = 0; c0 < CPT; c0 += 16) {
                 int lv[Tr::LEVELS][16];
@@ -412,7 +416,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
                     for (int L = Tr::LEVELS - 2; L >= 0; --L)
                         t += (long long)lv[L][j] * (long long)(1 << (7 * (Tr::LEVELS - 1 - L)));
-                    T[c0 + j] = t;
+                    T[c0 + j] = (TAcc)t;
                 }
             }
             tc_fence_before();

@@ -64,6 +64,8 @@ def test_layout_rejects_bad_arguments(L):
     assert layout(L, 4, 4, 4, slices=0)[0] == rg.cudaErrorInvalidValue
     assert layout(L, 4, 4, 4, slices=4)[0] == rg.cudaErrorInvalidValue
     assert layout(L, 4, 4, 4, batch=0)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 4, batch=70000)[0] == rg.cudaErrorInvalidValue
+    assert layout(L, 4, 4, 4, batch=65535)[0] == 0
 
 
 def test_k_bound_for_exact_int64(L):
