@@ -245,7 +245,11 @@ void launch_split(const float* src, bool k_major, const float* given_max, uint32
         else
             colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), ceil_div(K, COLMAX_K_PER_CTA), batch), PREPASS_THREADS, 0, st>>>(
                 src, maxbits, R, K, batch_stride);
-        split_kstrided_kernel<S><<<dim3(ceil_div(R, 32), Kp / BLOCK_K, batch), PREPASS_THREADS, 0, st>>>(
+        // about eight CTAs per SM in total; each walks over the k tiles of its 32 rows
+        const int r_blocks = ceil_div(R, 32), k_tiles = Kp / BLOCK_K;
+        int walkers = ceil_div(PLAN_SM_COUNT * 8, r_blocks * batch);
+        walkers = walkers < 1 ? 1 : (walkers > k_tiles ? k_tiles : walkers);
+        split_kstrided_kernel<S><<<dim3(r_blocks, walkers, batch), PREPASS_THREADS, 0, st>>>(
             src, maxbits, planes, expo, R, K, Kp, batch_stride);
     }
 }

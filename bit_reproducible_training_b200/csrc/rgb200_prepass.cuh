@@ -167,9 +167,9 @@ split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ giv
 // k-strided operand: element (r, k) at src[k*R + r]   (B without trans_b, A with trans_a).
 // Pass 1: column maxima over K with an integer atomicMax (|x| >= 0 orders like its bit pattern,
 // so the result is exact and order-free).  maxbits[batch][R] must be zero on entry.
-// grid = (ceil(R / 128), ceil(K / 256), batch), block = 256 threads = 32 column groups x 8 k-rows.
+// grid = (ceil(R / 128), ceil(K / 64), batch), block = 256 threads = 32 column groups x 8 k-rows.
 // ---------------------------------------------------------------------------------------------
-constexpr int COLMAX_K_PER_CTA = 256;
+constexpr int COLMAX_K_PER_CTA = 64;
 
 __global__ void __launch_bounds__(PREPASS_THREADS)
 colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ maxbits, int R, int K,
@@ -237,11 +237,12 @@ rowmax_kmajor_kernel(const float* __restrict__ src, float* __restrict__ out, int
     if ((threadIdx.x & 31) == 0) out[row] = m;
 }
 
-// Pass 2 for the k-strided operand: a 32 (r) x 128 (k) tile is read with r contiguous (16-byte loads
+// Pass 2 for the k-strided operand: 32 (r) x 128 (k) tiles are read with r contiguous (16-byte loads
 // where R allows), transposed through shared memory and written with k contiguous, 128 bytes per
 // row and plane.  Shared layout: tile[r][k] with the 16-byte column index XOR-ed by (r / 4) % 8, which
-// makes both the transposing stores and the row reads bank-conflict free.
-// grid = (ceil(R / 32), Kp / 128, batch)
+// makes both the transposing stores and the row reads bank-conflict free.  A CTA walks over several
+// k tiles of its 32 rows and loads the next tile into registers while it splits the current one.
+// grid = (ceil(R / 32), k-tile walkers <= Kp / 128, batch)
 template <int S>
 __global__ void __launch_bounds__(PREPASS_THREADS)
 split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict__ maxbits,
@@ -251,7 +252,8 @@ split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict_
     __shared__ int e_sh[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.z;
-    const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 128;
+    const int r0 = blockIdx.x * 32;
+    const int k_tiles = Kp / 128;
     const float* s = src + (size_t)b * src_batch_stride;
     const size_t plane_stride = (size_t)R * Kp;
     int8_t* out = planes + (size_t)b * S * plane_stride;
@@ -264,37 +266,65 @@ split_kstrided_kernel(const float* __restrict__ src, const uint32_t* __restrict_
         if (r < R && blockIdx.y == 0) expo[(size_t)b * R + r] = e;
     }
     const bool vec = (R & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) & 15) == 0);
-    if (vec) {
-        // a warp covers 4 k-rows x 32 r per load: lane = (k sub-row, group of four r)
-        const int kk4 = lane >> 3, rq = lane & 7, r = r0 + rq * 4;
-#pragma unroll 4
-        for (int kk = warp * 4 + kk4; kk < 128; kk += 32) {
-            const int k = k0 + kk;
-            float4 v = (r < R && k < K) ? __ldg(reinterpret_cast<const float4*>(s + (size_t)k * R + r))
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-            tile[slot(rq * 4 + 0, kk)] = v.x;
-            tile[slot(rq * 4 + 1, kk)] = v.y;
-            tile[slot(rq * 4 + 2, kk)] = v.z;
-            tile[slot(rq * 4 + 3, kk)] = v.w;
-        }
-    } else {
-        const int r = r0 + lane;
-#pragma unroll 4
-        for (int kk = warp; kk < 128; kk += 8) {
-            const int k = k0 + kk;
-            tile[slot(lane, kk)] = (r < R && k < K) ? __ldg(s + (size_t)k * R + r) : 0.0f;
-        }
-    }
-    __syncthreads();
-    // split: warp w takes rows w, w + 8, ...; lanes run along k in groups of four
+    // vector path: a warp covers 4 k-rows x 32 r per load, lane = (k sub-row, group of four r);
+    // scalar path: a warp covers one k-row, lane = r.  Either way a thread holds 16 values of a tile.
+    const int kk4 = lane >> 3, rq = lane & 7;
+    float4 reg[4];
+    auto load_tile = [&](int kt) {
+        const int k0 = kt * 128;
+        if (vec) {
+            const int r = r0 + rq * 4;
 #pragma unroll
-    for (int rr = warp; rr < 32; rr += 8) {
-        const int r = r0 + rr;
-        if (r >= R) continue;
-        const int e = e_sh[rr];
-        const QuantScale q = quant_scale(e, S);
-        const float4 v = *reinterpret_cast<const float4*>(&tile[slot(rr, lane * 4)]);
-        store_quad<S>(v, q, plain_row(e), out, plane_stride, (size_t)r * Kp + k0 + lane * 4);   // uniform over the warp
+            for (int i = 0; i < 4; ++i) {
+                const int k = k0 + warp * 4 + kk4 + 32 * i;
+                reg[i] = (r < R && k < K) ? __ldg(reinterpret_cast<const float4*>(s + (size_t)k * R + r))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        } else {
+            const int r = r0 + lane;
+            float* f = reinterpret_cast<float*>(reg);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int k = k0 + warp + 8 * i;
+                f[i] = (r < R && k < K) ? __ldg(s + (size_t)k * R + r) : 0.0f;
+            }
+        }
+    };
+    auto stage_tile = [&]() {
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int kk = warp * 4 + kk4 + 32 * i;
+                tile[slot(rq * 4 + 0, kk)] = reg[i].x;
+                tile[slot(rq * 4 + 1, kk)] = reg[i].y;
+                tile[slot(rq * 4 + 2, kk)] = reg[i].z;
+                tile[slot(rq * 4 + 3, kk)] = reg[i].w;
+            }
+        } else {
+            const float* f = reinterpret_cast<const float*>(reg);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) tile[slot(lane, warp + 8 * i)] = f[i];
+        }
+    };
+
+    int kt = blockIdx.y;
+    if (kt < k_tiles) load_tile(kt);
+    for (; kt < k_tiles; kt += gridDim.y) {
+        stage_tile();
+        __syncthreads();
+        const int next = kt + gridDim.y;
+        if (next < k_tiles) load_tile(next);            // in flight while this tile is split
+        // split: warp w takes rows w, w + 8, ...; lanes run along k in groups of four
+#pragma unroll
+        for (int rr = warp; rr < 32; rr += 8) {
+            const int r = r0 + rr;
+            if (r >= R) continue;
+            const int e = e_sh[rr];
+            const QuantScale q = quant_scale(e, S);
+            const float4 v = *reinterpret_cast<const float4*>(&tile[slot(rr, lane * 4)]);
+            store_quad<S>(v, q, plain_row(e), out, plane_stride, (size_t)r * Kp + kt * 128 + lane * 4);   // uniform over the warp
+        }
+        __syncthreads();                                 // the tile is rewritten by the next round
     }
 }
 
