@@ -212,6 +212,67 @@ def gemm_host(hA, hB, hC, dA, dB, dC, M, N, K, cfg, workspace, stream=None):
         hC.copy_(dC, non_blocking=True)
 
 
+class HostGemm:
+    """C = op(A) op(B) for operands and result in pinned HOST memory, with the PCIe copies overlapped.
+
+    B is copied first; A then travels in blocks of rows, and for each block the split pre-pass, the MMA
+    kernel and the copy of the finished rows of C back to the host run while the next block of A is
+    still on its way (three streams: copy-in, compute, copy-out).  Row blocks are independent
+    products (row scales and sums never cross rows), so the bits equal those of one call.
+    Device buffers, the workspace, streams and events are created once; a call allocates nothing.
+    With trans_a the rows of op(A) are not contiguous in host memory and the call falls back to
+    one copy, one run, one copy."""
+
+    def __init__(self, M, N, K, cfg=None, block_rows=512, device=None):
+        self.M, self.N, self.K, self.cfg = M, N, K, cfg or Config()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.block = M if self.cfg.trans_a else max(1, min(block_rows, M))
+        self.blocks = [(lo, min(M, lo + self.block)) for lo in range(0, M, self.block)]
+        rc, plan = make_plan(self.block, N, K, self.cfg)
+        if rc != cudaSuccess:
+            raise ReproGemmError(rc, "make_plan")
+        with torch.cuda.device(self.device):
+            self.dA = torch.empty(M * K, dtype=torch.float32, device=self.device)
+            self.dB = torch.empty(K * N, dtype=torch.float32, device=self.device)
+            self.dC = torch.empty(M * N, dtype=torch.float32, device=self.device)
+            self.ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=self.device)
+            self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+            self.ev_b = torch.cuda.Event()
+            self.ev_a = [torch.cuda.Event() for _ in self.blocks]
+            self.ev_c = [torch.cuda.Event() for _ in self.blocks]
+
+    def __call__(self, hA, hB, hC):
+        """Enqueues the whole product; on return the caller's current stream is ordered after the last
+        copy into hC (synchronise that stream, or record an event on it, to know when hC is ready)."""
+        M, N, K = self.M, self.N, self.K
+        cur = torch.cuda.current_stream(self.device)
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.wait_stream(cur)
+        hA, hB, hC = hA.view(-1), hB.view(-1), hC.view(-1)
+        with torch.cuda.stream(self.s_in):
+            self.dB.copy_(hB, non_blocking=True)
+            self.ev_b.record()
+            for (lo, hi), ev in zip(self.blocks, self.ev_a):
+                self.dA[lo * K:hi * K].copy_(hA[lo * K:hi * K], non_blocking=True)
+                ev.record()
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(self.ev_b)
+            for (lo, hi), ev_a, ev_c in zip(self.blocks, self.ev_a, self.ev_c):
+                self.s_run.wait_event(ev_a)
+                rc = repro_gemm_fp32_ws(self.dA[lo * K:hi * K], self.dB, self.dC[lo * N:hi * N], hi - lo, N, K, self.cfg,
+                                        self.ws, stream=self.s_run)
+                if rc != cudaSuccess:
+                    raise ReproGemmError(rc, "repro_gemm_fp32_ws")
+                ev_c.record()
+        with torch.cuda.stream(self.s_out):
+            for (lo, hi), ev_c in zip(self.blocks, self.ev_c):
+                self.s_out.wait_event(ev_c)
+                hC[lo * N:hi * N].copy_(self.dC[lo * N:hi * N], non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_in)
+        cur.wait_stream(self.s_run)
+
+
 # ------------------------------------------------------------------------------------------------
 # K-sharded building blocks (one K range per rank); see bit_reproducible_training_b200/sharded.py
 # ------------------------------------------------------------------------------------------------

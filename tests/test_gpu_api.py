@@ -222,3 +222,26 @@ def test_suite_tool_writes_reference_format(tmp_path):
     assert len(ops) == 21
     for f in ops:
         assert f[0] == "OP" and (f[3][3:], f[4][4:]) == SUITE_HASHES[f[1]]
+
+
+def test_host_buffer_pipeline_matches_single_call():
+    """Pinned host operands in, pinned host result out, row blocks overlapped with the copies: same bits
+    as one call, for plain and transposed storage (the latter falls back to a single block)."""
+    M, N, K = 1100, 260, 520
+    A, B = fx.hash_tool_inputs("wide", M, N, K)
+    want = oracle.gemm(A, B, M, N, K)
+    hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+    hC = torch.empty(M * N).pin_memory()
+    for block_rows in (128, 300, 4096):
+        pipe = rg.HostGemm(M, N, K, rg.Config(), block_rows=block_rows)
+        for _ in range(2):
+            hC.fill_(float("nan"))
+            pipe(hA, hB, hC)
+            torch.cuda.synchronize()
+            assert np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1)), block_rows
+    hAt = torch.from_numpy(np.ascontiguousarray(A.reshape(M, K).T).reshape(-1)).pin_memory()
+    pipe = rg.HostGemm(M, N, K, rg.Config(trans_a=True))
+    hC.fill_(float("nan"))
+    pipe(hAt, hB, hC)
+    torch.cuda.synchronize()
+    assert len(pipe.blocks) == 1 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
