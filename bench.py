@@ -7,7 +7,8 @@ epilogue) over one 4096 x 4096 x 4096, S = 3 GEMM with the wide-dynamic-range sy
 With N > 1 GPUs (torchrun, one rank per GPU) the default mode shards rows of A: every rank owns a
 4096-row block of a (4096 N) x 4096 x 4096 product and the whole B; no collective is on the data
 path (weak scaling).  --mode ksplit instead gives every rank a 4096-wide K range of a
-4096 x 4096 x (4096 N) product and reduces the exact INT64 partial sums with an NCCL all-reduce.
+4096 x 4096 x (4096 N) product and reduces the exact INT64 partial sums with NCCL; --mode
+ksplit-fused lets the MMA epilogue store the partial sums straight into the owning rank's memory.
 
 Prints one JSON line (rank 0).  `value` is 2 M N K / time summed over ranks with the inputs
 resident in HBM; `e2e` repeats the measurement through the host-buffer call (pinned host memory,
@@ -138,7 +139,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--mode", default="rows", choices=["rows", "ksplit"])
+    ap.add_argument("--mode", default="rows", choices=["rows", "ksplit", "ksplit-fused"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--check", action="store_true", help="also compare the output hash with the golden value")
     args = ap.parse_args()
@@ -181,7 +182,8 @@ def main():
     for evs in stage_ev:
         for e in evs:
             e.record()          # creates the handles the library records into
-    ks = sharded.KSplitState(M, N, K, world, cfg, dA, dB) if (args.mode == "ksplit" and world > 1) else None
+    ks = sharded.KSplitState(M, N, K, world, cfg, dA, dB, fused=args.mode == "ksplit-fused") \
+        if (args.mode != "rows" and world > 1) else None
 
     def step(events=None):
         if ks is not None:
@@ -267,7 +269,8 @@ def main():
                 "config": {"workload": "C=A.B fp32, M=N=K=4096 per GPU, S=3 int8 slices, wide-dynamic-range inputs "
                                        "(1% zeros, 0.1% subnormals), seed 3",
                            "sharding": "none" if world == 1 else ("rows of A, no collective" if ks is None else
-                                                                  "K ranges, NCCL int64 all-reduce"),
+                                                                  ("K ranges, NCCL int64 reduce-scatter + fp32 all-gather" if args.mode == "ksplit" else
+                                                                   "K ranges, epilogue peer stores into the row owners + fp32 all-gather")),
                            "l2": "512 MiB buffer written between timed iterations (L2 flush)"},
                 "clocks": clocks,
                 "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 4,

@@ -45,8 +45,10 @@ def lib():
     L.rgb200_gemm_fp32_batched_ws.argtypes = [fp, fp, fp, i, i, i, i, ll, ll, ll, cfgp, vp, C.c_size_t, vp,
                                               C.POINTER(vp)]
     L.rgb200_gemm_fp32_static.argtypes = [fp, fp, fp, i, i, i, cfgp, vp]
+    L.rgb200_selftest_bounded_wait.argtypes = [ll, C.POINTER(C.c_int), C.POINTER(ll), C.POINTER(C.c_int)]
     L.rgb200_absmax.argtypes = [fp, i, i, i, fp, vp]
     L.rgb200_gemm_partial_ws.argtypes = [fp, fp, fp, fp, vp, i, i, i, ll, cfgp, vp, C.c_size_t, vp]
+    L.rgb200_gemm_partial_scatter_ws.argtypes = [fp, fp, fp, fp, C.POINTER(vp), i, i, i, i, i, ll, cfgp, vp, C.c_size_t, vp]
     L.rgb200_round_partial.argtypes = [vp, i, fp, fp, fp, i, i, i, vp]
     L.rgb200_workspace_status.argtypes = [vp, C.POINTER(C.c_int)]
     L.rgb200_algo_name.argtypes = [i]

@@ -264,6 +264,8 @@ struct RunArgs {
     char* ws;
     cudaStream_t st;
     const cudaEvent_t* ev;
+    long long* const* scatter = nullptr;   // per-owner destination buffers of the INT64 sums (K-sharded), or null
+    int scatter_world = 0, scatter_rank = 0;
 };
 
 template <int S>
@@ -327,6 +329,15 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     P.m_tiles = ceil_div(L.M, BLOCK_M);
     P.n_tiles = ceil_div(L.N, tile_n);
     P.e0 = e0;
+    P.scatter_rows = 0; P.scatter_slot = 0;
+    for (int i = 0; i < 8; ++i) P.scatter[i] = nullptr;
+    if (a.scatter) {
+        P.scatter_rows = L.M / a.scatter_world;
+        P.scatter_slot = a.scatter_rank;
+        for (int i = 0; i < a.scatter_world; ++i) P.scatter[i] = a.scatter[i];
+        P.partial = a.scatter[a.scatter_rank];      // non-null marks the INT64 path; every row is redirected
+        P.C = nullptr;
+    }
     const long long tiles = (long long)L.batch * L.split * P.m_tiles * P.n_tiles;
     const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
     if (S == 1 && tile_n == 256)
@@ -540,6 +551,29 @@ int rgb200_gemm_partial_ws(const float* A, const float* B, const float* max_a, c
     return dispatch(L, a, *dev);
 }
 
+int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* max_a, const float* max_b,
+                                   long long* const* owner_buffers, int world, int rank, int M, int N, int K,
+                                   long long total_k, const rgb200_config* cfg, void* workspace, size_t workspace_bytes,
+                                   void* stream) {
+    if (!A || !B || !max_a || !max_b || !owner_buffers || !cfg) return cudaErrorInvalidValue;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || M % world != 0) return cudaErrorInvalidValue;
+    for (int i = 0; i < world; ++i)
+        if (!owner_buffers[i] || (reinterpret_cast<uintptr_t>(owner_buffers[i]) & 15)) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = plan_layout(M, N, K, total_k, 1, *cfg, true, L);
+    if (e != cudaSuccess) return e;
+    if (L.algo == RGB200_ALGO_REFERENCE) return cudaErrorNotSupported;
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
+    if (!workspace || workspace_bytes < L.total) return cudaErrorInvalidValue;
+    RunArgs a{A, B, nullptr, owner_buffers[rank], max_a, max_b, 0, 0, 0, cfg->trans_a != 0, cfg->trans_b != 0,
+              static_cast<char*>(workspace), static_cast<cudaStream_t>(stream), nullptr};
+    a.scatter = owner_buffers;
+    a.scatter_world = world;
+    a.scatter_rank = rank;
+    return dispatch(L, a, *dev);
+}
+
 int rgb200_round_partial(const long long* T, int parts, const float* max_a, const float* max_b, float* C, int M, int N,
                          int slices, void* stream) {
     if (!T || !max_a || !max_b || !C || parts <= 0 || M <= 0 || N <= 0 || slices < 1 || slices > 3)
@@ -552,6 +586,26 @@ int rgb200_round_partial(const long long* T, int parts, const float* max_a, cons
     round_partial_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         T, parts, total, nullptr, nullptr, max_a, max_b, C, M, N, 1, (long long)total, -14 * (slices - 1));
     return cudaGetLastError();
+}
+
+int rgb200_selftest_bounded_wait(long long limit_clocks, int* status, long long* waited_clocks, int* both_left) {
+    if (!status || !waited_clocks || !both_left || limit_clocks <= 0 || limit_clocks > 2000000000ll) return cudaErrorInvalidValue;
+    const DeviceInfo* dev = nullptr;
+    cudaError_t e = check_device(RGB200_ALGO_TENSORCORE, &dev);
+    if (e != cudaSuccess) return e;
+    void* base = nullptr;
+    if ((e = static_workspace_address(&base)) != cudaSuccess) return e;     // scratch from the fixed array: no allocation
+    int* d_status = static_cast<int*>(base);
+    long long* d_out = reinterpret_cast<long long*>(static_cast<char*>(base) + 64);
+    if ((e = cudaMemset(base, 0, 256)) != cudaSuccess) return e;
+    bounded_wait_probe_kernel<<<1, 64>>>(d_status, limit_clocks, d_out);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e;
+    long long out[3];
+    if ((e = cudaMemcpy(status, d_status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess) return e;
+    if ((e = cudaMemcpy(out, d_out, sizeof out, cudaMemcpyDeviceToHost)) != cudaSuccess) return e;
+    *both_left = (out[0] == 1 && out[1] == 1) ? 1 : 0;
+    *waited_clocks = out[2];
+    return cudaSuccess;
 }
 
 uint64_t rgb200_fnv1a64(const void* data, size_t bytes, uint64_t h) {

@@ -89,6 +89,11 @@ struct GemmParams {
     int split;               // number of K ranges
     int m_tiles, n_tiles;
     int e0;                  // -14 (S - 1)
+    // Row-block scatter of the INT64 output (K-sharded multi-GPU): rows [o * scatter_rows, (o+1) * scatter_rows)
+    // go to scatter[o], the buffer of the rank that owns them (its own or a peer's memory over NVLink), into
+    // slot `scatter_slot` of that buffer's [slots][scatter_rows][N] layout.  scatter_rows == 0: off.
+    long long* scatter[8];
+    int scatter_rows, scatter_slot;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -116,14 +121,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false after the limit or once another role has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long limit = WAIT_LIMIT_CLOCKS) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = clock64();
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CLOCKS) {
+            if (clock64() - t0 > limit) {
                 atomicCAS(status, 0, code);
                 *abort_flag = 1;
                 __threadfence_block();
@@ -428,6 +434,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             if (!row_ok || col0 >= P.N) continue;
             if (P.partial) {
                 long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col0;
+                if (P.scatter_rows) {          // plain stores into the owner's memory; no multicast, no TMA
+                    const int owner = row / P.scatter_rows;
+                    dst = P.scatter[owner] + ((size_t)P.scatter_slot * P.scatter_rows + (row - owner * P.scatter_rows)) * P.N + col0;
+                }
                 if (col0 + CPT <= P.N) {
                     if ((reinterpret_cast<uintptr_t>(dst) & 8) == 0) store_row_i64<CPT, 0>(dst, T);
                     else store_row_i64<CPT, 1>(dst, T);
@@ -487,6 +497,31 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, Tr::TMEM_COLS);
+    }
+}
+
+// Self-test of the bounded wait: one warp waits on a barrier that nothing will ever complete, with a
+// short limit.  Lane 0 must give up after `limit` clocks, store `code` in *status and raise the abort
+// flag; lane 1, waiting with the full limit, must leave early because it sees that flag.
+// out[0] = lane 0 returned false, out[1] = lane 1 returned false, out[2] = clocks lane 0 waited.
+__global__ void bounded_wait_probe_kernel(int* status, long long limit, long long* out) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long t0 = clock64();
+        bool ok = mbar_wait(b, 0, &abort_flag, status, STATUS_WAIT_FULL, limit);
+        out[0] = ok ? 0 : 1;
+        out[2] = clock64() - t0;
+    } else if (threadIdx.x == 32) {
+        bool ok = mbar_wait(b, 0, &abort_flag, status, STATUS_WAIT_EMPTY);
+        out[1] = ok ? 0 : 1;
     }
 }
 

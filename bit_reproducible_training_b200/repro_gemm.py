@@ -301,6 +301,22 @@ def gemm_partial(A, B, max_a, max_b, M, N, K, total_k, cfg):
     return T
 
 
+def gemm_partial_scatter(A, B, max_a, max_b, owner_ptrs, world, rank, M, N, K, total_k, cfg):
+    """Exact INT64 sums over this rank's K range, stored by row block into the owners' receive buffers
+    (owner_ptrs: device addresses valid on this device; slot `rank` of each [world][M/world][N] buffer)."""
+    c = cfg.c()
+    p = _lib.Plan()
+    rc = _lib.lib().rgb200_make_plan_partial(M, N, K, total_k, C.byref(c), C.byref(p))
+    if rc != cudaSuccess:
+        raise ReproGemmError(rc, "make_plan_partial")
+    ws = _workspace(p.workspace_bytes, A.device)
+    ptrs = (C.c_void_p * world)(*[C.c_void_p(int(x)) for x in owner_ptrs])
+    rc = _lib.lib().rgb200_gemm_partial_scatter_ws(_ptr(A), _ptr(B), _ptr(max_a), _ptr(max_b), ptrs, world, rank, M, N, K,
+                                                  total_k, C.byref(c), _ptr(ws), ws.numel(), _stream(None))
+    if rc != cudaSuccess:
+        raise ReproGemmError(rc, "gemm_partial_scatter_ws")
+
+
 def round_partial(T, max_a, max_b, M, N, slices):
     """C = single rounding of (sum over the leading axis of T) * 2^(eA + eB - 14 (S - 1))."""
     T = T.contiguous()

@@ -91,13 +91,62 @@ def gemm_k_sharded(A_k, B_k, M, N, k_local, total_k, cfg, group=None, backend=No
     return backend.round_partial(T, max_a, max_b, M, N, cfg.slices)
 
 
+class FusedKShard:
+    """K-sharded product whose reduction starts inside the MMA kernel.
+
+    Every rank owns M / world rows of the result.  The MMA kernel's epilogue stores the exact INT64
+    sums of each row block directly into the owner's receive buffer (plain peer stores over NVLink,
+    issued tile by tile while the rest of the product is still being computed), so the reduce-scatter
+    of the collective form needs no separate pass over the data: after a stream-ordered barrier each
+    owner adds its `world` slots, rounds once, and an FP32 all-gather distributes C.  Integer addition
+    is exact in any order, so the bits equal the single-GPU product.
+
+    The receive buffers live in torch symmetric memory (peer-mapped at rendezvous); the object is
+    created once per shape and reused, nothing is mapped per call.  NCCL only.
+    """
+
+    def __init__(self, M, N, cfg, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if M % self.world or self.world > 8:
+            raise ValueError("the fused K-shard needs M divisible by a world size of at most 8")
+        self.M, self.N, self.cfg, self.rows = M, N, cfg, M // self.world
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.slots = symm_mem.empty((self.world, self.rows, N), dtype=torch.int64, device=dev)
+        self.handle = symm_mem.rendezvous(self.slots, self.group)
+        self.owner_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.launches_per_step = 8
+
+    def __call__(self, A_k, B_k, k_local, total_k):
+        cfg, M, N = self.cfg, self.M, self.N
+        max_a = rg.absmax(A_k, M, k_local, cfg.trans_a)
+        max_b = rg.absmax(B_k, N, k_local, not cfg.trans_b)
+        dist.all_reduce(max_a, op=dist.ReduceOp.MAX, group=self.group)
+        dist.all_reduce(max_b, op=dist.ReduceOp.MAX, group=self.group)
+        rg.gemm_partial_scatter(A_k, B_k, max_a, max_b, self.owner_ptrs, self.world, self.rank, M, N, k_local, total_k, cfg)
+        # stream-ordered barrier: no rank reads its slots before every rank's kernel has finished writing them
+        dist.all_reduce(self.token, group=self.group)
+        lo = self.rank * self.rows
+        C_own = rg.round_partial(self.slots, max_a[lo:lo + self.rows].contiguous(), max_b, self.rows, N, cfg.slices)
+        C = torch.empty((M, N), dtype=torch.float32, device=C_own.device)
+        # the gather also keeps a fast rank's next product from overwriting slots a slow owner still reads
+        dist.all_gather_into_tensor(C, C_own, group=self.group)
+        return C
+
+
 class KSplitState:
     """Benchmark helper: this rank's operands are one K range of an M x N x (K * world) product."""
     launches_per_step = 8   # row max, column max, split A, maxima->bits + split B, MMA, rounding (+ the memset)
 
-    def __init__(self, M, N, K, world, cfg, dA, dB):
+    def __init__(self, M, N, K, world, cfg, dA, dB, fused=False):
         self.M, self.N, self.K, self.world, self.cfg, self.dA, self.dB = M, N, K, world, cfg, dA, dB
+        self.fused = FusedKShard(M, N, cfg) if fused else None
 
     def step(self, dC):
-        out = gemm_k_sharded(self.dA, self.dB, self.M, self.N, self.K, self.K * self.world, self.cfg)
+        if self.fused is not None:
+            out = self.fused(self.dA, self.dB, self.K, self.K * self.world)
+        else:
+            out = gemm_k_sharded(self.dA, self.dB, self.M, self.N, self.K, self.K * self.world, self.cfg)
         dC.copy_(out.reshape(-1))

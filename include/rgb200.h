@@ -105,11 +105,33 @@ int rgb200_gemm_partial_ws(const float* A, const float* B, const float* max_a, c
 int rgb200_round_partial(const long long* T, int parts, const float* max_a, const float* max_b, float* C,
                          int M, int N, int slices, void* stream);
 
+/* Step 2 fused with the first half of the reduction (no counterpart in the reference): instead of
+ * writing its INT64 sums locally and leaving the exchange to a collective, the MMA kernel's epilogue
+ * stores each block of M / world rows straight into the memory of the rank that owns those rows
+ * (plain peer stores over NVLink while other tiles are still being computed).  owner_buffers[o] is
+ * the device address, valid on THIS device, of rank o's receive buffer laid out
+ * [world slots][M / world rows][N] INT64; this rank writes slot `rank` of every buffer (its own
+ * included).  After all ranks' kernels have completed (any stream-ordered cross-rank barrier), owner o
+ * calls rgb200_round_partial(buffer_o, world, max_a + o * M / world, max_b, C_rows, M / world, N, S).
+ * world <= 8, M % world == 0; buffers 16-byte aligned.  The buffers are peer-mapped memory supplied
+ * by the caller (for example torch symmetric memory); this library maps nothing itself. */
+int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* max_a, const float* max_b,
+                                   long long* const* owner_buffers, int world, int rank, int M, int N, int K,
+                                   long long total_k, const rgb200_config* cfg, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
 /* Call after the stream has been synchronised.  *status = 0 if the last run that used this workspace
  * completed, else the code a kernel left when one of its bounded waits expired (it then stopped
  * without hanging; the output is incomplete).  The reference reports kernel failures only through
  * cudaGetLastError (repro_gemm_cuda/repro_gemm.cu:527); this is the same channel for that one case. */
 int rgb200_workspace_status(const void* workspace, int* status);
+
+/* Self-test of the kernels' bounded waits (no counterpart in the reference, which has no waits): a probe
+ * kernel waits on a barrier that nothing completes, with `limit_clocks` (at most 2e9) as its limit.
+ * *status receives the code the waiting role stored when it gave up (2), *waited_clocks how long it
+ * waited, *both_left = 1 if a second role waiting with the normal two-second limit also left at once
+ * because it saw the first one's abort flag.  The device stays usable; nothing hangs or traps. */
+int rgb200_selftest_bounded_wait(long long limit_clocks, int* status, long long* waited_clocks, int* both_left);
 
 /* Allocation-free variant of rgb200_gemm_fp32 (it has no counterpart in the reference, whose
  * convenience call repro_gemm_fp32 allocates and frees its workspace on every call).

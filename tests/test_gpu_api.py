@@ -245,3 +245,45 @@ def test_host_buffer_pipeline_matches_single_call():
     pipe(hAt, hB, hC)
     torch.cuda.synchronize()
     assert len(pipe.blocks) == 1 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
+
+
+def test_bounded_wait_expires_and_reports():
+    """Failure detection without a fault: a wait that nothing will satisfy runs into its (short) limit,
+    leaves a status code, makes the other waiting role leave too, and the device keeps working."""
+    import ctypes as C
+    from bit_reproducible_training_b200 import _lib
+    status, waited, both = C.c_int(-1), C.c_longlong(0), C.c_int(0)
+    limit = 2_000_000                                   # about a millisecond
+    rc = _lib.lib().rgb200_selftest_bounded_wait(limit, C.byref(status), C.byref(waited), C.byref(both))
+    assert rc == 0
+    assert status.value == 2                            # the code of the role that gave up
+    assert both.value == 1                              # the second role saw the abort flag and left
+    assert limit < waited.value < 200 * limit           # it did wait for the limit, and not much longer
+    n = 256                                             # the context is intact: a GEMM still runs and is exact
+    g = fx.Rng(12)
+    A, B = g.normal(n * n), g.normal(n * n)
+    got = rg.gemm(dev(A), dev(B), n, n, n).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), oracle.gemm(A, B, n, n, n).view(np.uint32))
+
+
+def test_scatter_epilogue_emulated_on_one_gpu():
+    """The row-block scatter of the INT64 sums, with three "ranks" run one after another on one GPU
+    and all receive buffers local: each owner's slots, added and rounded once, give its rows of C."""
+    world, M, N, K = 3, 384, 200, 900
+    A, B = fx.hash_tool_inputs("stress", M, N, K)
+    want = oracle.gemm(A, B, M, N, K)
+    Am, Bm = A.reshape(M, K), B.reshape(K, N)
+    rows = M // world
+    bufs = [torch.full((world, rows, N), -7, dtype=torch.int64, device="cuda") for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    cuts = [sharded.shard_range(K, world, r) for r in range(world)]
+    shards = [(dev(Am[:, lo:hi]), dev(Bm[lo:hi]), hi - lo) for lo, hi in cuts]
+    cfg = rg.Config()
+    max_a = torch.stack([rg.absmax(a, M, k, False) for a, _, k in shards]).amax(0)
+    max_b = torch.stack([rg.absmax(b, N, k, True) for _, b, k in shards]).amax(0)
+    for r, (a, b, k) in enumerate(shards):
+        rg.gemm_partial_scatter(a, b, max_a, max_b, ptrs, world, r, M, N, k, K, cfg)
+    torch.cuda.synchronize()
+    for o in range(world):
+        got = rg.round_partial(bufs[o], max_a[o * rows:(o + 1) * rows].contiguous(), max_b, rows, N, 3).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want[o * rows:(o + 1) * rows].view(np.uint32)), o

@@ -53,6 +53,12 @@ def worker(rank, world, port, n, want_hash, out_dir):
                                      torch.from_numpy(np.ascontiguousarray(B[klo:khi].T)).cuda(),
                                      n, n, khi - klo, n, cfg_t)
         assert "%016x" % rg.fnv1a64(C_t) == want_hash, "K-sharded (transposed storage) result differs"
+        # K ranges with the reduction started inside the MMA epilogue (peer stores into the row owners)
+        fused = sharded.FusedKShard(n, n, cfg)
+        for _ in range(2):
+            C_f = fused(torch.from_numpy(np.ascontiguousarray(A[:, klo:khi])).cuda(),
+                        torch.from_numpy(np.ascontiguousarray(B[klo:khi])).cuda(), khi - klo, n)
+            assert "%016x" % rg.fnv1a64(C_f) == want_hash, "fused K-shard result differs"
         torch.cuda.synchronize()
         open(os.path.join(out_dir, "ok.%d" % rank), "w").close()
     finally:
