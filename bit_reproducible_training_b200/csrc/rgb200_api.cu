@@ -254,6 +254,20 @@ void launch_split(const float* src, bool k_major, const float* given_max, uint32
     }
 }
 
+// Picks the four-wide form of the rounding kernel when rows, strides and base addresses allow it.
+void launch_round(const long long* partial, int parts, size_t part_stride, const int* ea, const int* eb,
+                  const float* max_a, const float* max_b, float* C, int M, int N, int batch, long long stride_c, int e0,
+                  int sm_count, cudaStream_t st) {
+    const size_t total = (size_t)batch * M * N;
+    const bool vec = N % 4 == 0 && part_stride % 4 == 0 && stride_c % 4 == 0 &&
+                     (reinterpret_cast<uintptr_t>(partial) & 31) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+    const size_t items = vec ? total / 4 : total;
+    const size_t want = (items + 255) / 256, cap = (size_t)sm_count * 32;
+    const int blocks = (int)(want < cap ? want : cap);
+    if (vec) round_partial_kernel<true><<<blocks, 256, 0, st>>>(partial, parts, part_stride, ea, eb, max_a, max_b, C, M, N, batch, stride_c, e0);
+    else round_partial_kernel<false><<<blocks, 256, 0, st>>>(partial, parts, part_stride, ea, eb, max_a, max_b, C, M, N, batch, stride_c, e0);
+}
+
 struct RunArgs {
     const float *A, *B;
     float* C;
@@ -349,9 +363,7 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     record(2);
     if (L.use_partial_ws) {
         const size_t total = (size_t)L.batch * L.M * L.N;
-        const int blocks = (int)((total + 255) / 256 < (size_t)dev.sm_count * 16 ? (total + 255) / 256 : (size_t)dev.sm_count * 16);
-        round_partial_kernel<<<blocks, 256, 0, a.st>>>(part, L.split, total, ea, eb, nullptr, nullptr, a.C, L.M, L.N, L.batch,
-                                                        a.stride_c, e0);
+        launch_round(part, L.split, total, ea, eb, nullptr, nullptr, a.C, L.M, L.N, L.batch, a.stride_c, e0, dev.sm_count, a.st);
     }
     record(3);
     return cudaGetLastError();
@@ -582,9 +594,8 @@ int rgb200_round_partial(const long long* T, int parts, const float* max_a, cons
     cudaError_t e = check_device(RGB200_ALGO_TENSORCORE, &dev);
     if (e != cudaSuccess) return e;
     const size_t total = (size_t)M * N;
-    const size_t want = (total + 255) / 256, cap = (size_t)dev->sm_count * 16;
-    round_partial_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        T, parts, total, nullptr, nullptr, max_a, max_b, C, M, N, 1, (long long)total, -14 * (slices - 1));
+    launch_round(T, parts, total, nullptr, nullptr, max_a, max_b, C, M, N, 1, (long long)total, -14 * (slices - 1),
+                 dev->sm_count, static_cast<cudaStream_t>(stream));
     return cudaGetLastError();
 }
 

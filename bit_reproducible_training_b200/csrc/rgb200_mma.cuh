@@ -219,6 +219,16 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& P, long long t
     return c;
 }
 
+// 32-byte global stores (one full sector per lane and instruction); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_256(uint32_t* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                              uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h) : "memory");
+}
+__device__ __forceinline__ void st_global_256(long long* p, long long a, long long b, long long c, long long d) {
+    asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(p), "l"(a), "l"(b), "l"(c), "l"(d) : "memory");
+}
+
 // Stores CPT consecutive values of one row whose start is HEAD elements before a 16-byte boundary:
 // HEAD scalar stores, then 16-byte stores, then the scalar rest.  Rows of C are 16-byte aligned only
 // when N % 4 == 0 (and the base pointer is); for ragged N the alignment changes from row to row.
@@ -439,7 +449,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     dst = P.scatter[owner] + ((size_t)P.scatter_slot * P.scatter_rows + (row - owner * P.scatter_rows)) * P.N + col0;
                 }
                 if (col0 + CPT <= P.N) {
-                    if ((reinterpret_cast<uintptr_t>(dst) & 8) == 0) store_row_i64<CPT, 0>(dst, T);
+                    if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+                        for (int j = 0; j < CPT; j += 4)
+                            st_global_256(dst + j, (long long)T[j], (long long)T[j + 1], (long long)T[j + 2], (long long)T[j + 3]);
+                    } else if ((reinterpret_cast<uintptr_t>(dst) & 8) == 0) store_row_i64<CPT, 0>(dst, T);
                     else store_row_i64<CPT, 1>(dst, T);
                 } else {
 #pragma unroll
@@ -462,7 +476,16 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     }
                 };
                 const int past = (int)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3);    // elements past a 16-byte boundary
-                if (past == 0 && col0 + CPT <= P.N) {
+                if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && col0 + CPT <= P.N) {
+                    // sector-aligned row segment: round eight, store one full 32-byte sector
+#pragma unroll
+                    for (int j = 0; j < CPT; j += 8) {
+                        uint32_t r[4], q[4];
+                        round4(j, r);
+                        round4(j + 4, q);
+                        st_global_256(dst + j, r[0], r[1], r[2], r[3], q[0], q[1], q[2], q[3]);
+                    }
+                } else if (past == 0 && col0 + CPT <= P.N) {
                     // aligned row segment: round four, store sixteen bytes, so stores overlap the next roundings
 #pragma unroll
                     for (int j = 0; j < CPT; j += 4) {
@@ -553,19 +576,43 @@ __global__ void gemm_int64_check_kernel(const int8_t* __restrict__ qa, const int
 
 // C = round(sum over `parts` INT64 partials); the reference's reduce_round (repro_gemm.cu:156-165).
 // partial is [parts][batch*M*N]; exponents either precomputed (ea/eb) or derived from maxima.
-__global__ void round_partial_kernel(const long long* __restrict__ partial, int parts, size_t part_stride,
-                                     const int* __restrict__ ea, const int* __restrict__ eb,
-                                     const float* __restrict__ max_a, const float* __restrict__ max_b,
-                                     float* __restrict__ C, int M, int N, int batch, long long stride_c, int e0) {
-    const size_t total = (size_t)batch * M * N;
+// VEC: four consecutive columns per thread with 32-byte loads and 16-byte stores (N % 4 == 0, aligned
+// buffers, dense C); otherwise one element per thread.  Grid-stride loop.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+round_partial_kernel(const long long* __restrict__ partial, int parts, size_t part_stride,
+                     const int* __restrict__ ea, const int* __restrict__ eb,
+                     const float* __restrict__ max_a, const float* __restrict__ max_b,
+                     float* __restrict__ C, int M, int N, int batch, long long stride_c, int e0) {
+    constexpr int W = VEC ? 4 : 1;
+    const size_t per_mat = (size_t)M * N;
+    const size_t total = (size_t)batch * per_mat / W;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        long long t = 0;
-        for (int p = 0; p < parts; ++p) t += partial[(size_t)p * part_stride + i];
-        const size_t b = i / ((size_t)M * N), rc = i - b * (size_t)M * N;
+        const size_t idx = i * W;
+        long long t[W];
+#pragma unroll
+        for (int j = 0; j < W; ++j) t[j] = 0;
+        for (int p = 0; p < parts; ++p) {
+            const long long* src = partial + (size_t)p * part_stride + idx;
+            if (VEC) {
+                longlong4 v = *reinterpret_cast<const longlong4*>(src);
+                t[0] += v.x; t[W > 1 ? 1 : 0] += v.y; t[W > 2 ? 2 : 0] += v.z; t[W > 3 ? 3 : 0] += v.w;
+            } else {
+                t[0] += src[0];
+            }
+        }
+        const size_t b = idx / per_mat, rc = idx - b * per_mat;
         const int r = (int)(rc / N), c = (int)(rc - (size_t)r * N);
-        const int e_r = ea ? ea[b * M + r] : scale_exponent(max_a[b * M + r]);
-        const int e_c = eb ? eb[b * N + c] : scale_exponent(max_b[b * N + c]);
-        C[b * (size_t)stride_c + (size_t)r * N + c] = bits_f32(round_to_f32_bits(t, e_r + e_c + e0));
+        const int e_r = (ea ? ea[b * M + r] : scale_exponent(max_a[b * M + r])) + e0;
+        uint32_t o[W];
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+            const int e_c = eb ? eb[b * N + c + j] : scale_exponent(max_b[b * N + c + j]);
+            o[j] = round_to_f32_bits(t[j], e_r + e_c);
+        }
+        float* dst = C + b * (size_t)stride_c + (size_t)r * N + c;
+        if (VEC) *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[W > 1 ? 1 : 0], o[W > 2 ? 2 : 0], o[W > 3 ? 3 : 0]);
+        else dst[0] = bits_f32(o[0]);
     }
 }
 
