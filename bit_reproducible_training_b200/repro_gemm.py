@@ -276,9 +276,10 @@ class HostGemm:
 # ------------------------------------------------------------------------------------------------
 # K-sharded building blocks (one K range per rank); see bit_reproducible_training_b200/sharded.py
 # ------------------------------------------------------------------------------------------------
-def absmax(X, R, K, k_strided):
-    """max over k of |op(X)[r, k]| as a float32 [R] tensor."""
-    out = torch.empty(R, dtype=torch.float32, device=X.device)
+def absmax(X, R, K, k_strided, out=None):
+    """max over k of |op(X)[r, k]| as a float32 [R] tensor (written into `out` when given)."""
+    if out is None:
+        out = torch.empty(R, dtype=torch.float32, device=X.device)
     rc = _lib.lib().rgb200_absmax(_ptr(X), R, K, int(k_strided), _ptr(out), _stream(None))
     if rc != cudaSuccess:
         raise ReproGemmError(rc, "absmax")

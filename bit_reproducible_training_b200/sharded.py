@@ -117,22 +117,25 @@ class FusedKShard:
         self.handle = symm_mem.rendezvous(self.slots, self.group)
         self.owner_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.token = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.launches_per_step = 8
+        self.maxima = torch.empty(M + N, dtype=torch.float32, device=dev)
+        self.launches_per_step = 7     # row max, column max, split A, maxima->bits + split B, MMA, rounding
 
-    def __call__(self, A_k, B_k, k_local, total_k):
+    def __call__(self, A_k, B_k, k_local, total_k, out=None):
         cfg, M, N = self.cfg, self.M, self.N
-        max_a = rg.absmax(A_k, M, k_local, cfg.trans_a)
-        max_b = rg.absmax(B_k, N, k_local, not cfg.trans_b)
-        dist.all_reduce(max_a, op=dist.ReduceOp.MAX, group=self.group)
-        dist.all_reduce(max_b, op=dist.ReduceOp.MAX, group=self.group)
+        # one buffer for both sets of maxima: a single max all-reduce instead of two
+        maxima = self.maxima
+        rg.absmax(A_k, M, k_local, cfg.trans_a, out=maxima[:M])
+        rg.absmax(B_k, N, k_local, not cfg.trans_b, out=maxima[M:])
+        dist.all_reduce(maxima, op=dist.ReduceOp.MAX, group=self.group)
+        max_a, max_b = maxima[:M], maxima[M:]
         rg.gemm_partial_scatter(A_k, B_k, max_a, max_b, self.owner_ptrs, self.world, self.rank, M, N, k_local, total_k, cfg)
         # stream-ordered barrier: no rank reads its slots before every rank's kernel has finished writing them
         dist.all_reduce(self.token, group=self.group)
         lo = self.rank * self.rows
-        C_own = rg.round_partial(self.slots, max_a[lo:lo + self.rows].contiguous(), max_b, self.rows, N, cfg.slices)
-        C = torch.empty((M, N), dtype=torch.float32, device=C_own.device)
+        C_own = rg.round_partial(self.slots, max_a[lo:lo + self.rows], max_b, self.rows, N, cfg.slices)
+        C = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=C_own.device)
         # the gather also keeps a fast rank's next product from overwriting slots a slow owner still reads
-        dist.all_gather_into_tensor(C, C_own, group=self.group)
+        dist.all_gather_into_tensor(C.view(M, N), C_own, group=self.group)
         return C
 
 
@@ -143,10 +146,12 @@ class KSplitState:
     def __init__(self, M, N, K, world, cfg, dA, dB, fused=False):
         self.M, self.N, self.K, self.world, self.cfg, self.dA, self.dB = M, N, K, world, cfg, dA, dB
         self.fused = FusedKShard(M, N, cfg) if fused else None
+        if self.fused is not None:
+            self.launches_per_step = self.fused.launches_per_step
 
     def step(self, dC):
         if self.fused is not None:
-            out = self.fused(self.dA, self.dB, self.K, self.K * self.world)
-        else:
-            out = gemm_k_sharded(self.dA, self.dB, self.M, self.N, self.K, self.K * self.world, self.cfg)
+            self.fused(self.dA, self.dB, self.K, self.K * self.world, out=dC)
+            return
+        out = gemm_k_sharded(self.dA, self.dB, self.M, self.N, self.K, self.K * self.world, self.cfg)
         dC.copy_(out.reshape(-1))
