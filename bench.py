@@ -133,6 +133,66 @@ def reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def auxiliary_workload(args):
+    """Times one of the other four configurations on one GPU (device-resident inputs, CUDA events,
+    L2 flushed between steps) and checks its output hash against the golden file."""
+    import torch
+    from bit_reproducible_training_b200 import fixtures as fx
+    from bit_reproducible_training_b200 import repro_gemm as rg
+    torch.cuda.set_device(0)
+    cases = {"c1": fx.config1, "c2": fx.config2, "c4": fx.config4, "c5": fx.config5}[args.workload]()
+    with open(os.path.join(ROOT, "tests", "golden", "gemm_hashes.json")) as f:
+        golden = {(r["name"], r["S"]): r["out_hash"] for r in json.load(f)}
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    prepared, flops = [], 0.0
+    for c in cases:
+        batch = c.get("batch", 1)
+        M, N, K = c["M"], c["N"], c["K"]
+        cfg = rg.Config(slices=SLICES, trans_a=c["trans_a"], trans_b=c["trans_b"])
+        rc, plan = rg.make_plan(M, N, K, cfg, batch=batch)
+        if rc != 0:
+            raise rg.ReproGemmError(rc, "make_plan")
+        prepared.append((c, cfg, batch, torch.from_numpy(c["A"]).cuda(), torch.from_numpy(c["B"]).cuda(),
+                         torch.empty(batch * M * N, dtype=torch.float32, device="cuda"),
+                         torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")))
+        flops += 2.0 * batch * M * N * K
+
+    def step():
+        for c, cfg, batch, dA, dB, dC, ws in prepared:
+            M, N, K = c["M"], c["N"], c["K"]
+            if batch == 1:
+                rc = rg.repro_gemm_fp32_ws(dA, dB, dC, M, N, K, cfg, ws)
+            else:
+                rc = rg.repro_gemm_fp32_batched_ws(dA, dB, dC, M, N, K, batch, M * K, K * N, M * N, cfg, ws)
+            if rc != 0:
+                raise rg.ReproGemmError(rc, c["name"])
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev:
+        flush.zero_()
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    ok = True
+    for c, cfg, batch, dA, dB, dC, ws in prepared:
+        name = c["name"] + (".b%d" % batch if "batch" in c else "")
+        want = golden.get((name, SLICES))
+        ok = ok and want is not None and ("%016x" % rg.fnv1a64(dC)) == want
+    print(json.dumps({"metric": "bit-exact FP32 GEMM TFLOP/s (2MNK/t), S=3", "value": flops / (ms * 1e-3) / 1e12,
+                      "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                      "ms_per_step": ms, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+                      "auxiliary": True, "output_matches_golden": ok,
+                      "config": {"workload": args.workload + ": " + ", ".join(
+                          "%s %s%dx%dx%d" % (c["name"], ("%d x " % c["batch"]) if "batch" in c else "", c["M"], c["N"], c["K"])
+                          for c in cases), "l2": "512 MiB buffer written between timed iterations (L2 flush)"}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,6 +202,9 @@ def main():
     ap.add_argument("--mode", default="rows", choices=["rows", "ksplit", "ksplit-fused"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--check", action="store_true", help="also compare the output hash with the golden value")
+    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="c3 (default) is the headline 4096^3 workload; the others time the remaining configurations "
+                         "on one GPU and print a reduced line (no e2e, no CPU baseline)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -149,6 +212,10 @@ def main():
 
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.workload != "c3":
+        if rank == 0:
+            auxiliary_workload(args)
         return
 
     import numpy as np
