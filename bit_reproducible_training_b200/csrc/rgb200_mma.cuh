@@ -444,7 +444,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             if (!row_ok || col0 >= P.N) continue;
             if (P.partial) {
                 long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col0;
-                if (P.scatter_rows) {          // plain stores into the owner's memory; no multicast, no TMA
+                if (P.scatter_rows) {          // ordinary global stores into the owner's memory (its own or a peer's)
                     const int owner = row / P.scatter_rows;
                     dst = P.scatter[owner] + ((size_t)P.scatter_slot * P.scatter_rows + (row - owner * P.scatter_rows)) * P.N + col0;
                 }
