@@ -301,7 +301,11 @@ def main():
         pre = [e[0].elapsed_time(e[1]) for e in stage_ev]
         mma = [e[1].elapsed_time(e[2]) for e in stage_ev]
         fin = [e[2].elapsed_time(e[3]) for e in stage_ev]
-        stages = {"prepass_ms": statistics.mean(pre), "mma_ms": statistics.mean(mma), "final_ms": statistics.mean(fin)}
+        def spread(v):      # median [min, p90], the form the reference's stage benchmark prints
+            v = sorted(v)
+            return {"median": statistics.median(v), "min": v[0], "p90": v[min(len(v) - 1, int(0.9 * len(v)))]}
+        stages = {"prepass_ms": statistics.mean(pre), "mma_ms": statistics.mean(mma), "final_ms": statistics.mean(fin),
+                  "prepass_ms_spread": spread(pre), "mma_ms_spread": spread(mma), "step_ms_spread": spread(step_ms)}
 
     # ---------------- end to end: host buffers in, host buffer out, copies inside the timed region
     e2e_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]

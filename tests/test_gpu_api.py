@@ -106,6 +106,18 @@ def test_long_k_is_cut_into_int32_safe_ranges():
     B1 = np.full(K1 * 8, -127.0, dtype=np.float32)
     got = rg.gemm(dev(A1), dev(B1), 8, 8, K1).cpu().numpy()
     assert np.array_equal(got.view(np.uint32), oracle.gemm(A1, B1, 8, 8, K1).view(np.uint32))
+    # every element with digits (-126, -64, -64): the middle level gains 2*126*64 + 64*64 = 20224 per k,
+    # 2 133 066 368 over the whole pass, within 0.7 % of the INT32 limit.  156 output tiles keep the
+    # planner from cutting K by itself, so this really is one accumulation pass.
+    M2, N2 = 1536, 832
+    rc, plan = rg.make_plan(M2, N2, K1, rg.Config())
+    assert rc == 0 and plan.split_k == 1
+    A2 = np.full(M2 * K1, -2072640.0, dtype=np.float32)
+    B2 = np.full(K1 * N2, -2072640.0, dtype=np.float32)
+    got = rg.gemm(dev(A2), dev(B2), M2, N2, K1).cpu().numpy()
+    want = oracle.round_partials(np.full((1, 1, 1), 2072640 * 2072640 * K1, dtype=np.int64),
+                                 np.float32([2072640.0]), np.float32([2072640.0]), 1, 1, 3)
+    assert (got.view(np.uint32) == want.view(np.uint32)[0, 0]).all()      # every output is the same exact sum
 
 
 @pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
