@@ -49,6 +49,9 @@ def lib():
     L.rgb200_absmax.argtypes = [fp, i, i, i, fp, vp]
     L.rgb200_gemm_partial_ws.argtypes = [fp, fp, fp, fp, vp, i, i, i, ll, cfgp, vp, C.c_size_t, vp]
     L.rgb200_gemm_partial_scatter_ws.argtypes = [fp, fp, fp, fp, C.POINTER(vp), i, i, i, i, i, ll, cfgp, vp, C.c_size_t, vp]
+    L.rgb200_scatter_buffer_elems.argtypes = [i, i, i, i]
+    L.rgb200_scatter_buffer_elems.restype = C.c_size_t
+    L.rgb200_round_scattered.argtypes = [vp, i, fp, fp, fp, i, i, i, vp]
     L.rgb200_round_partial.argtypes = [vp, i, fp, fp, fp, i, i, i, vp]
     L.rgb200_workspace_status.argtypes = [vp, C.POINTER(C.c_int)]
     L.rgb200_algo_name.argtypes = [i]

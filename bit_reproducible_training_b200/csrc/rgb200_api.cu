@@ -568,9 +568,9 @@ int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* 
                                    long long total_k, const rgb200_config* cfg, void* workspace, size_t workspace_bytes,
                                    void* stream) {
     if (!A || !B || !max_a || !max_b || !owner_buffers || !cfg) return cudaErrorInvalidValue;
-    if (world < 1 || world > 8 || rank < 0 || rank >= world || M % world != 0) return cudaErrorInvalidValue;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || M % (world * BLOCK_M) != 0) return cudaErrorInvalidValue;
     for (int i = 0; i < world; ++i)
-        if (!owner_buffers[i] || (reinterpret_cast<uintptr_t>(owner_buffers[i]) & 15)) return cudaErrorInvalidValue;
+        if (!owner_buffers[i] || (reinterpret_cast<uintptr_t>(owner_buffers[i]) & 31)) return cudaErrorInvalidValue;
     Layout L;
     cudaError_t e = plan_layout(M, N, K, total_k, 1, *cfg, true, L);
     if (e != cudaSuccess) return e;
@@ -584,6 +584,32 @@ int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* 
     a.scatter_world = world;
     a.scatter_rank = rank;
     return dispatch(L, a, *dev);
+}
+
+size_t rgb200_scatter_buffer_elems(int M, int N, int world, int slices) {
+    if (M <= 0 || N <= 0 || world < 1 || world > 8 || slices < 1 || slices > 3 || M % (world * BLOCK_M) != 0) return 0;
+    const int nt = tile_n_for(slices, N);
+    return (size_t)world * (M / world) * ceil_div(N, nt) * nt;
+}
+
+int rgb200_round_scattered(const long long* buffer, int world, const float* max_a_own, const float* max_b, float* C_own,
+                           int rows_own, int N, int slices, void* stream) {
+    if (!buffer || !max_a_own || !max_b || !C_own || world < 1 || world > 8 || rows_own <= 0 || rows_own % BLOCK_M != 0 ||
+        N <= 0 || slices < 1 || slices > 3 || (reinterpret_cast<uintptr_t>(buffer) & 31))
+        return cudaErrorInvalidValue;
+    const DeviceInfo* dev = nullptr;
+    cudaError_t e = check_device(RGB200_ALGO_TENSORCORE, &dev);
+    if (e != cudaSuccess) return e;
+    const int nt = tile_n_for(slices, N), n_tiles = ceil_div(N, nt);
+    const size_t chunks = (size_t)rows_own * n_tiles * nt / 4;
+    const size_t want = (chunks + 255) / 256, cap = (size_t)dev->sm_count * 32;
+    const int blocks = (int)(want < cap ? want : cap);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int e0 = -14 * (slices - 1);
+    if (nt == 256) round_scattered_kernel<256><<<blocks, 256, 0, st>>>(buffer, world, max_a_own, max_b, C_own, rows_own, N, n_tiles, e0);
+    else if (nt == 96) round_scattered_kernel<96><<<blocks, 256, 0, st>>>(buffer, world, max_a_own, max_b, C_own, rows_own, N, n_tiles, e0);
+    else round_scattered_kernel<64><<<blocks, 256, 0, st>>>(buffer, world, max_a_own, max_b, C_own, rows_own, N, n_tiles, e0);
+    return cudaGetLastError();
 }
 
 int rgb200_round_partial(const long long* T, int parts, const float* max_a, const float* max_b, float* C, int M, int N,

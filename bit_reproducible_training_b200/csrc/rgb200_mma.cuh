@@ -91,7 +91,9 @@ struct GemmParams {
     int e0;                  // -14 (S - 1)
     // Row-block scatter of the INT64 output (K-sharded multi-GPU): rows [o * scatter_rows, (o+1) * scatter_rows)
     // go to scatter[o], the buffer of the rank that owns them (its own or a peer's memory over NVLink), into
-    // slot `scatter_slot` of that buffer's [slots][scatter_rows][N] layout.  scatter_rows == 0: off.
+    // slot `scatter_slot`.  A slot is stored tile by tile in the order the epilogue produces it (see
+    // scatter_offset), so every store instruction of a warp covers one contiguous kilobyte.
+    // scatter_rows == 0: off; otherwise a multiple of 128.
     long long* scatter[8];
     int scatter_rows, scatter_slot;
 };
@@ -251,6 +253,16 @@ __device__ __forceinline__ void store_row_i64(long long* dst, const TAcc (&t)[CP
     for (int i = 0; i < BODY; ++i)
         *reinterpret_cast<longlong2*>(dst + HEAD + 2 * i) = make_longlong2((long long)t[HEAD + 2 * i], (long long)t[HEAD + 2 * i + 1]);
     if (HEAD) dst[CPT - 1] = t[CPT - 1];
+}
+
+// Tile-native layout of one slot of a scatter buffer.  A slot holds the owner's rows as
+// [row tile][column tile][w = 0..7][store j][lane 0..31][4] INT64, where w = 4 * (column half) + (TMEM lane
+// quarter), i.e. block w covers quarter w % 4 (rows 32 (w % 4) .. +31 of the tile) and column half w / 4, and store j covers columns
+// 4 j .. 4 j + 3 of that half.  Returns the element offset of (tile, warp, j, lane) inside the slot.
+template <int NT>
+__host__ __device__ __forceinline__ size_t scatter_offset(int m_local, int n_blk, int n_tiles, int w, int j, int lane) {
+    constexpr int CPT = NT / 2;
+    return ((((size_t)m_local * n_tiles + n_blk) * 8 + w) * (CPT / 4) + j) * 128 + (size_t)lane * 4;
 }
 
 // Position in the flattened (tile, k block) sequence a CTA works through.
@@ -441,12 +453,19 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             if (blockIdx.x == 0 && tile_it < 5 && threadIdx.x == 64) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 3] = clock64();
 #endif
             // phase 2: one rounding per output (or the raw sums), overlapped with the next tile's MMAs
-            if (!row_ok || col0 >= P.N) continue;
+            if (!P.scatter_rows && (!row_ok || col0 >= P.N)) continue;
             if (P.partial) {
                 long long* dst = P.partial + (((size_t)tc.z * P.batch + tc.batch) * P.M + row) * P.N + col0;
                 if (P.scatter_rows) {          // ordinary global stores into the owner's memory (its own or a peer's)
                     const int owner = row / P.scatter_rows;
-                    dst = P.scatter[owner] + ((size_t)P.scatter_slot * P.scatter_rows + (row - owner * P.scatter_rows)) * P.N + col0;
+                    const int m_local = tc.m_blk - owner * (P.scatter_rows / BLOCK_M);
+                    const size_t slot_elems = (size_t)P.scatter_rows * P.n_tiles * NT;
+                    long long* base = P.scatter[owner] + (size_t)P.scatter_slot * slot_elems;
+#pragma unroll
+                    for (int j = 0; j < CPT / 4; ++j)
+                        st_global_256(base + scatter_offset<NT>(m_local, tc.n_blk, P.n_tiles, (half << 2) | quarter, j, lane),
+                                      (long long)T[4 * j], (long long)T[4 * j + 1], (long long)T[4 * j + 2], (long long)T[4 * j + 3]);
+                    continue;
                 }
                 if (col0 + CPT <= P.N) {
                     if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
@@ -613,6 +632,40 @@ round_partial_kernel(const long long* __restrict__ partial, int parts, size_t pa
         float* dst = C + b * (size_t)stride_c + (size_t)r * N + c;
         if (VEC) *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[W > 1 ? 1 : 0], o[W > 2 ? 2 : 0], o[W > 3 ? 3 : 0]);
         else dst[0] = bits_f32(o[0]);
+    }
+}
+
+// Owner-side finish of the scattered K-shard reduction: adds the `world` slots of a tile-native scatter
+// buffer (see scatter_offset), rounds once and writes the owner's rows of C densely ([rows][N]).
+// A warp reads one contiguous kilobyte per slot (lane = row within a 32-row group, four columns each).
+template <int NT>
+__global__ void __launch_bounds__(256)
+round_scattered_kernel(const long long* __restrict__ buffer, int world, const float* __restrict__ max_a,
+                       const float* __restrict__ max_b, float* __restrict__ C, int rows, int N, int n_tiles, int e0) {
+    constexpr int CPT = NT / 2;
+    const size_t slot_elems = (size_t)rows * n_tiles * NT;
+    const size_t chunks = slot_elems / 4;                       // 32-byte chunks per slot
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < chunks; t += (size_t)gridDim.x * blockDim.x) {
+        const int lane = (int)(t & 31);
+        size_t u = t >> 5;
+        const int j = (int)(u % (CPT / 4)); u /= (CPT / 4);
+        const int w = (int)(u & 7); u >>= 3;
+        const int n_blk = (int)(u % n_tiles);
+        const int m_local = (int)(u / n_tiles);
+        const int row = m_local * BLOCK_M + (w & 3) * 32 + lane;
+        const int col = n_blk * NT + (w >> 2) * CPT + 4 * j;
+        if (col >= N) continue;
+        long long s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+        for (int p = 0; p < world; ++p) {
+            const longlong4 v = *reinterpret_cast<const longlong4*>(buffer + (size_t)p * slot_elems + t * 4);
+            s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+        }
+        const int e_r = scale_exponent(max_a[row]) + e0;
+        float* dst = C + (size_t)row * N + col;
+        const long long sum[4] = {s0, s1, s2, s3};
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (col + q < N) dst[q] = bits_f32(round_to_f32_bits(sum[q], e_r + scale_exponent(max_b[col + q])));
     }
 }
 

@@ -304,7 +304,7 @@ def gemm_partial(A, B, max_a, max_b, M, N, K, total_k, cfg):
 
 def gemm_partial_scatter(A, B, max_a, max_b, owner_ptrs, world, rank, M, N, K, total_k, cfg):
     """Exact INT64 sums over this rank's K range, stored by row block into the owners' receive buffers
-    (owner_ptrs: device addresses valid on this device; slot `rank` of each [world][M/world][N] buffer)."""
+    (owner_ptrs: device addresses valid on this device; slot `rank` of each buffer of scatter_buffer_elems)."""
     c = cfg.c()
     p = _lib.Plan()
     rc = _lib.lib().rgb200_make_plan_partial(M, N, K, total_k, C.byref(c), C.byref(p))
@@ -316,6 +316,22 @@ def gemm_partial_scatter(A, B, max_a, max_b, owner_ptrs, world, rank, M, N, K, t
                                                   total_k, C.byref(c), _ptr(ws), ws.numel(), _stream(None))
     if rc != cudaSuccess:
         raise ReproGemmError(rc, "gemm_partial_scatter_ws")
+
+
+def scatter_buffer_elems(M, N, world, slices):
+    """INT64 elements of one rank's receive buffer for gemm_partial_scatter (0: shape not supported)."""
+    return int(_lib.lib().rgb200_scatter_buffer_elems(M, N, world, slices))
+
+
+def round_scattered(buffer, world, max_a_own, max_b, rows_own, N, slices, out=None):
+    """Owner-side finish of the scattered reduction: sum of the `world` slots, one rounding, dense rows of C."""
+    if out is None:
+        out = torch.empty((rows_own, N), dtype=torch.float32, device=buffer.device)
+    rc = _lib.lib().rgb200_round_scattered(_ptr(buffer), world, _ptr(max_a_own), _ptr(max_b), _ptr(out), rows_own, N,
+                                          slices, _stream(None))
+    if rc != cudaSuccess:
+        raise ReproGemmError(rc, "round_scattered")
+    return out
 
 
 def round_partial(T, max_a, max_b, M, N, slices):

@@ -95,8 +95,9 @@ class FusedKShard:
     """K-sharded product whose reduction starts inside the MMA kernel.
 
     Every rank owns M / world rows of the result.  The MMA kernel's epilogue stores the exact INT64
-    sums of each row block directly into the owner's receive buffer (plain peer stores over NVLink,
-    issued tile by tile while the rest of the product is still being computed), so the reduce-scatter
+    sums of each row block directly into the owner's receive buffer (ordinary peer stores over NVLink,
+    one contiguous kilobyte per warp-wide store thanks to a tile-native buffer layout, issued tile by
+    tile while the rest of the product is still being computed), so the reduce-scatter
     of the collective form needs no separate pass over the data: after a stream-ordered barrier each
     owner adds its `world` slots, rounds once, and an FP32 all-gather distributes C.  Integer addition
     is exact in any order, so the bits equal the single-GPU product.
@@ -109,11 +110,12 @@ class FusedKShard:
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        if M % self.world or self.world > 8:
-            raise ValueError("the fused K-shard needs M divisible by a world size of at most 8")
+        elems = rg.scatter_buffer_elems(M, N, self.world, cfg.slices)
+        if elems == 0:
+            raise ValueError("the fused K-shard needs M to be a multiple of 128 * world and at most 8 ranks")
         self.M, self.N, self.cfg, self.rows = M, N, cfg, M // self.world
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.slots = symm_mem.empty((self.world, self.rows, N), dtype=torch.int64, device=dev)
+        self.slots = symm_mem.empty((elems,), dtype=torch.int64, device=dev)
         self.handle = symm_mem.rendezvous(self.slots, self.group)
         self.owner_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.token = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -132,7 +134,7 @@ class FusedKShard:
         # stream-ordered barrier: no rank reads its slots before every rank's kernel has finished writing them
         dist.all_reduce(self.token, group=self.group)
         lo = self.rank * self.rows
-        C_own = rg.round_partial(self.slots, max_a[lo:lo + self.rows], max_b, self.rows, N, cfg.slices)
+        C_own = rg.round_scattered(self.slots, self.world, max_a[lo:lo + self.rows], max_b, self.rows, N, cfg.slices)
         C = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=C_own.device)
         # the gather also keeps a fast rank's next product from overwriting slots a slow owner still reads
         dist.all_gather_into_tensor(C.view(M, N), C_own, group=self.group)

@@ -108,13 +108,19 @@ int rgb200_round_partial(const long long* T, int parts, const float* max_a, cons
 /* Step 2 fused with the first half of the reduction (no counterpart in the reference): instead of
  * writing its INT64 sums locally and leaving the exchange to a collective, the MMA kernel's epilogue
  * stores each block of M / world rows straight into the memory of the rank that owns those rows
- * (plain peer stores over NVLink while other tiles are still being computed).  owner_buffers[o] is
- * the device address, valid on THIS device, of rank o's receive buffer laid out
- * [world slots][M / world rows][N] INT64; this rank writes slot `rank` of every buffer (its own
- * included).  After all ranks' kernels have completed (any stream-ordered cross-rank barrier), owner o
- * calls rgb200_round_partial(buffer_o, world, max_a + o * M / world, max_b, C_rows, M / world, N, S).
- * world <= 8, M % world == 0; buffers 16-byte aligned.  The buffers are peer-mapped memory supplied
- * by the caller (for example torch symmetric memory); this library maps nothing itself. */
+ * (ordinary peer stores over NVLink while other tiles are still being computed).  owner_buffers[o]
+ * is the device address, valid on THIS device, of rank o's receive buffer of
+ * rgb200_scatter_buffer_elems(M, N, world, S) INT64 elements: `world` slots, slot `rank` written by this
+ * call (on every owner, its own included).  A slot keeps the owner's rows tile by tile in the order
+ * the epilogue produces them, so each warp-wide store covers one contiguous kilobyte.
+ * After all ranks' kernels have completed (any stream-ordered cross-rank barrier), owner o calls
+ * rgb200_round_scattered(buffer_o, world, max_a + o * M / world, max_b, C_rows, M / world, N, S), which
+ * adds the slots, rounds once and writes its rows of C densely.
+ * world <= 8, M a multiple of 128 * world, buffers 32-byte aligned.  The buffers are peer-mapped
+ * memory supplied by the caller (for example torch symmetric memory); this library maps nothing. */
+size_t rgb200_scatter_buffer_elems(int M, int N, int world, int slices);
+int rgb200_round_scattered(const long long* buffer, int world, const float* max_a_own, const float* max_b,
+                           float* C_own, int rows_own, int N, int slices, void* stream);
 int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* max_a, const float* max_b,
                                    long long* const* owner_buffers, int world, int rank, int M, int N, int K,
                                    long long total_k, const rgb200_config* cfg, void* workspace,

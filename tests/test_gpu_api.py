@@ -281,21 +281,24 @@ def test_bounded_wait_expires_and_reports():
 def test_scatter_epilogue_emulated_on_one_gpu():
     """The row-block scatter of the INT64 sums, with three "ranks" run one after another on one GPU
     and all receive buffers local: each owner's slots, added and rounded once, give its rows of C."""
-    world, M, N, K = 3, 384, 200, 900
-    A, B = fx.hash_tool_inputs("stress", M, N, K)
-    want = oracle.gemm(A, B, M, N, K)
-    Am, Bm = A.reshape(M, K), B.reshape(K, N)
-    rows = M // world
-    bufs = [torch.full((world, rows, N), -7, dtype=torch.int64, device="cuda") for _ in range(world)]
-    ptrs = [b.data_ptr() for b in bufs]
-    cuts = [sharded.shard_range(K, world, r) for r in range(world)]
-    shards = [(dev(Am[:, lo:hi]), dev(Bm[lo:hi]), hi - lo) for lo, hi in cuts]
-    cfg = rg.Config()
-    max_a = torch.stack([rg.absmax(a, M, k, False) for a, _, k in shards]).amax(0)
-    max_b = torch.stack([rg.absmax(b, N, k, True) for _, b, k in shards]).amax(0)
-    for r, (a, b, k) in enumerate(shards):
-        rg.gemm_partial_scatter(a, b, max_a, max_b, ptrs, world, r, M, N, k, K, cfg)
-    torch.cuda.synchronize()
-    for o in range(world):
-        got = rg.round_partial(bufs[o], max_a[o * rows:(o + 1) * rows].contiguous(), max_b, rows, N, 3).cpu().numpy()
-        assert np.array_equal(got.view(np.uint32), want[o * rows:(o + 1) * rows].view(np.uint32)), o
+    for world, M, N, K, S in ((3, 384, 200, 900, 3), (2, 512, 1000, 300, 1), (2, 256, 330, 260, 2)):
+        A, B = fx.hash_tool_inputs("stress", M, N, K)
+        want = oracle.gemm(A, B, M, N, K, S=S)
+        Am, Bm = A.reshape(M, K), B.reshape(K, N)
+        rows = M // world
+        elems = rg.scatter_buffer_elems(M, N, world, S)
+        assert elems >= world * rows * N
+        bufs = [torch.full((elems,), -7, dtype=torch.int64, device="cuda") for _ in range(world)]
+        ptrs = [b.data_ptr() for b in bufs]
+        cuts = [sharded.shard_range(K, world, r) for r in range(world)]
+        shards = [(dev(Am[:, lo:hi]), dev(Bm[lo:hi]), hi - lo) for lo, hi in cuts]
+        cfg = rg.Config(slices=S)
+        max_a = torch.stack([rg.absmax(a, M, k, False) for a, _, k in shards]).amax(0)
+        max_b = torch.stack([rg.absmax(b, N, k, True) for _, b, k in shards]).amax(0)
+        for r, (a, b, k) in enumerate(shards):
+            rg.gemm_partial_scatter(a, b, max_a, max_b, ptrs, world, r, M, N, k, K, cfg)
+        torch.cuda.synchronize()
+        for o in range(world):
+            got = rg.round_scattered(bufs[o], world, max_a[o * rows:(o + 1) * rows], max_b, rows, N, S).cpu().numpy()
+            assert np.array_equal(got.view(np.uint32), want[o * rows:(o + 1) * rows].view(np.uint32)), (world, S, o)
+    assert rg.scatter_buffer_elems(300, 64, 2, 3) == 0          # rows per owner must be whole 128-row tiles
