@@ -157,8 +157,9 @@ int rgb200_selftest_bounded_wait(long long limit_clocks, int* status, long long*
  *   - 2 (cudaErrorMemoryAllocation) is returned, and nothing is launched, when the problem needs more
  *     workspace than the fixed array holds (rgb200_layout reports the need; 32 MiB covers for example
  *     2048 x 2048 x 1024 or 1024 x 3072 x 768 at S = 3).  Other errors are those of rgb200_gemm_fp32_ws.
- *   - The first call on each device looks up the array's device address; make that first call outside
- *     any stream capture.
+ *   - The first call on each device looks up the array's device address (and, like the first call of
+ *     any entry point here, creates the library's per-device helper stream and events and sets kernel
+ *     attributes); make that first call outside any stream capture.  Later calls only enqueue work.
  *   - All calls share the one array.  The library re-zeroes the part that must start at zero on every
  *     call, but two calls that overlap on the GPU (different streams, or different threads without
  *     ordering) race on it: issue them on one stream, or order them with events. */
