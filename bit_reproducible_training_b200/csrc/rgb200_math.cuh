@@ -94,19 +94,10 @@ RGB_HD int fixed_point(float x, const QuantScale& q) {
     return X > q.lim ? q.lim : (X < -q.lim ? -q.lim : X);
 }
 
-// Balanced base-128 digits, most significant first: X = sum d[p] * 128^(S-1-p), |d[0]| <= 127,
-// d[p>0] in [-64, 63].  Any exact split gives the same T; this one keeps every slice-pair sum of a
+// Digits: X is split into S balanced base-128 digits, most significant first, X = sum d[p] * 128^(S-1-p)
+// with |d[0]| <= 127 and d[p>0] in [-64, 63] (the split itself lives in the pre-pass, which extracts
+// biased 7-bit fields).  Any exact split gives the same T; this one keeps every slice-pair sum of a
 // level within INT32 for 105517 values of k (S = 3), see max_k_per_pass().
-template <int S>
-RGB_HD void split_digits(int X, int (&d)[S]) {
-#pragma unroll
-    for (int p = S - 1; p >= 1; --p) {
-        int low = ((X + 64) & 127) - 64;
-        d[p] = low;
-        X = (X - low) >> 7;
-    }
-    d[0] = X;
-}
 
 // Largest number of k values whose level sums are guaranteed to fit INT32 in one accumulation pass.
 // Level L collects the digit products d_p(x) * d_q(y) with p + q = L; per k its magnitude is at most

@@ -333,9 +333,5 @@ __global__ void maxima_to_bits_kernel(const float* __restrict__ in, uint32_t* __
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = f32_bits(fmaxf(in[i], 0.0f));
 }
-__global__ void bits_to_maxima_kernel(const uint32_t* __restrict__ in, float* __restrict__ out, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = bits_f32(in[i]);
-}
 
 }  // namespace rgb200

@@ -198,20 +198,6 @@ def gemm_batched(A, B, batch, M, N, K, trans_a=False, trans_b=False, slices=3):
     return out
 
 
-def gemm_host(hA, hB, hC, dA, dB, dC, M, N, K, cfg, workspace, stream=None):
-    """End-to-end call with HOST buffers: pinned hA, hB -> device, run, device -> pinned hC, all on
-    one stream.  The caller synchronises.  Device and pinned buffers are supplied so nothing is
-    allocated per call."""
-    s = stream if stream is not None else torch.cuda.current_stream()
-    with torch.cuda.stream(s):
-        dA.copy_(hA, non_blocking=True)
-        dB.copy_(hB, non_blocking=True)
-        rc = repro_gemm_fp32_ws(dA, dB, dC, M, N, K, cfg, workspace, stream=s)
-        if rc != cudaSuccess:
-            raise ReproGemmError(rc, "repro_gemm_fp32_ws")
-        hC.copy_(dC, non_blocking=True)
-
-
 class HostGemm:
     """C = op(A) op(B) for operands and result in pinned HOST memory, with the PCIe copies overlapped.
 
