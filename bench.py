@@ -29,6 +29,8 @@ sys.path.insert(0, ROOT)
 SIZE = 4096
 SLICES = 3
 METRIC = "bit-exact FP32 GEMM TFLOP/s (2MNK/t), S=3, 4096^3"
+WORKLOAD = ("C=A.B fp32, M=N=K=4096 per GPU, S=3 int8 slices, wide-dynamic-range inputs "
+            "(1% zeros, 0.1% subnormals), seed 3")
 NOMINAL_INT8_TOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one MMA-kernel launch at this workload, from the
 # ncu capture summarised in profiles/gemm_i8_tcgen05_4096cubed_S3.md (193.0 MB read + 53.3 MB written)
@@ -127,7 +129,7 @@ def reference_arm(args, rank):
     line = {"impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "config": {"workload": "4096x4096x4096 S=3 wide-dynamic-range GEMM; CPU sample: " + info["sample"]},
+            "config": {"workload": WORKLOAD, "sharding": "none (rank 0 only, host cores)", "cpu_sample": info["sample"]},
             "cpu_baseline": info,
             "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -337,8 +339,7 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-                "config": {"workload": "C=A.B fp32, M=N=K=4096 per GPU, S=3 int8 slices, wide-dynamic-range inputs "
-                                       "(1% zeros, 0.1% subnormals), seed 3",
+                "config": {"workload": WORKLOAD,
                            "sharding": "none" if world == 1 else ("rows of A, no collective" if ks is None else
                                                                   ("K ranges, NCCL int64 reduce-scatter + fp32 all-gather" if args.mode == "ksplit" else
                                                                    "K ranges, epilogue peer stores into the row owners + fp32 all-gather")),
