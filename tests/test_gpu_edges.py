@@ -129,3 +129,26 @@ def test_batched_ragged_shapes():
         for b in range(batch):
             want = oracle.gemm(A[b * M * K:(b + 1) * M * K], B[b * K * N:(b + 1) * K * N], M, N, K, ta, tb, 3)
             assert np.array_equal(out[b].view(np.uint32), want.view(np.uint32)), (b, ta, tb)
+
+
+def test_batched_with_k_ranges_and_every_slice_count():
+    """Batches, explicit K ranges (INT64 partials per batch and range) and padded strides together."""
+    batch, M, N, K = 4, 140, 200, 700
+    g = fx.Rng(707)
+    sa, sb, sc = M * K + 8, K * N + 4, M * N + 12
+    A, B = g.normal(batch * sa), g.wide(batch * sb, -6, 6)
+    dA, dB = dev(A), dev(B)
+    for S in (1, 2, 3):
+        for split in (1, 3):
+            cfg = rg.Config(slices=S, split_k=split)
+            rc, plan = rg.make_plan(M, N, K, cfg, batch=batch)
+            assert rc == 0 and plan.split_k == split
+            ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+            out = torch.full((batch * sc,), float("nan"), device="cuda")
+            assert rg.repro_gemm_fp32_batched_ws(dA, dB, out, M, N, K, batch, sa, sb, sc, cfg, ws) == 0
+            torch.cuda.synchronize()
+            o = out.cpu().numpy()
+            for b in range(batch):
+                want = oracle.gemm(A[b * sa:b * sa + M * K], B[b * sb:b * sb + K * N], M, N, K, S=S)
+                assert np.array_equal(o[b * sc:b * sc + M * N].view(np.uint32), want.view(np.uint32).reshape(-1)), (S, split, b)
+                assert np.isnan(o[b * sc + M * N:(b + 1) * sc]).all()
