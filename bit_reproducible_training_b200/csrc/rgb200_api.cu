@@ -218,27 +218,43 @@ cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, in
 // ------------------------------------------------------------------------------------------
 // Launch sequence
 // ------------------------------------------------------------------------------------------
+// Launches the k-contiguous split for one operand (second.src == nullptr) or for two operands of the same
+// row length in one grid.
+template <int S>
+void launch_kmajor(const KmajorOperand& first, const KmajorOperand& second, int K, int Kp, int batch, int* zero_word,
+                   cudaStream_t st) {
+    const bool two = second.src != nullptr;
+    auto aligned_op = [&](const KmajorOperand& o) {
+        return (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(o.src) & 15) == 0) && (o.batch_stride % 4 == 0);
+    };
+    const bool aligned = aligned_op(first) && (!two || aligned_op(second));
+    const int nq = Kp / 4;     // float4 chunks per padded row
+#define RGB_KMAJOR(TPR, CH, VEC)                                                                              \
+    do {                                                                                                      \
+        const int rpc = PREPASS_THREADS / TPR;                                                                \
+        const int b1 = ceil_div(first.R, rpc), b2 = two ? ceil_div(second.R, rpc) : 0;                        \
+        split_kmajor_kernel<S, TPR, CH, VEC><<<dim3(b1 + b2, batch), PREPASS_THREADS, 0, st>>>(               \
+            first, second, b1, K, Kp, zero_word);                                                             \
+    } while (0)
+    if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS) RGB_KMAJOR(256, 1, false);
+    else if (nq <= 32 * 2) RGB_KMAJOR(32, 2, true);
+    else if (nq <= 32 * 4) RGB_KMAJOR(32, 4, true);
+    else if (nq <= 64 * 4) RGB_KMAJOR(64, 4, true);
+    else if (nq <= 128 * 4) RGB_KMAJOR(128, 4, true);
+    else if (nq <= 256 * 4) RGB_KMAJOR(256, 4, true);
+    else if (nq <= 256 * 8) RGB_KMAJOR(256, 8, true);
+    else RGB_KMAJOR(256, 16, true);
+#undef RGB_KMAJOR
+}
+
 // One operand through the pre-pass.  k_major: element (r, k) at src[r*K + k].
 template <int S>
 void launch_split(const float* src, bool k_major, const float* given_max, uint32_t* maxbits, int8_t* planes, int* expo,
                   int R, int K, int Kp, int batch, long long batch_stride, cudaStream_t st) {
     if (k_major) {
-        const bool aligned = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (batch_stride % 4 == 0);
-        const int nq = Kp / 4;     // float4 chunks per padded row
-#define RGB_KMAJOR(TPR, CH)                                                                                   \
-        split_kmajor_kernel<S, TPR, CH, true><<<dim3(ceil_div(R, PREPASS_THREADS / TPR), batch), PREPASS_THREADS, 0, st>>>( \
-            src, given_max, planes, expo, R, K, Kp, batch_stride)
-        if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS)
-            split_kmajor_kernel<S, 256, 1, false><<<dim3(R, batch), PREPASS_THREADS, 0, st>>>(
-                src, given_max, planes, expo, R, K, Kp, batch_stride);
-        else if (nq <= 32 * 2) RGB_KMAJOR(32, 2);
-        else if (nq <= 32 * 4) RGB_KMAJOR(32, 4);
-        else if (nq <= 64 * 4) RGB_KMAJOR(64, 4);
-        else if (nq <= 128 * 4) RGB_KMAJOR(128, 4);
-        else if (nq <= 256 * 4) RGB_KMAJOR(256, 4);
-        else if (nq <= 256 * 8) RGB_KMAJOR(256, 8);
-        else RGB_KMAJOR(256, 16);
-#undef RGB_KMAJOR
+        const KmajorOperand op{src, given_max, planes, expo, R, batch_stride};
+        const KmajorOperand none{nullptr, nullptr, nullptr, nullptr, 0, 0};
+        launch_kmajor<S>(op, none, K, Kp, batch, nullptr, st);
     } else {
         if (given_max)
             maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);
@@ -295,7 +311,18 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     long long* part = L.use_partial_ws ? reinterpret_cast<long long*>(a.ws + L.part) : a.T_out;
     const int e0 = -14 * (S - 1);
 
-    cudaError_t e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
+    cudaError_t e = cudaSuccess;
+    // Both operands k-contiguous (the forward product of a linear layer, C = A B^T): one launch splits both
+    // and clears the status word; no column maxima are needed, hence no memset either.
+    const bool both_kmajor = !a.trans_a && a.trans_b;
+    if (both_kmajor) {
+        record(0);
+        const KmajorOperand opa{a.A, a.max_a, qa, ea, L.M, a.stride_a};
+        const KmajorOperand opb{a.B, a.max_b, qb, eb, L.N, a.stride_b};
+        launch_kmajor<S>(opa, opb, L.K, L.Kp, L.batch, status, a.st);
+        record(1);
+    } else {
+    e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
     if (e != cudaSuccess) return e;
     record(0);
     // The two operands are independent until the MMA kernel.  For large operands A's split runs on a side
@@ -318,6 +345,7 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
             return cudaErrorUnknown;          // the side stream could not be joined: do not run on half-ordered data
     }
     record(1);
+    }
 
     if (L.algo == RGB200_ALGO_REFERENCE) {
         gemm_int64_check_kernel<S><<<dim3(ceil_div(L.N, 16), ceil_div(L.M, 16), L.batch), dim3(16, 16), 0, a.st>>>(

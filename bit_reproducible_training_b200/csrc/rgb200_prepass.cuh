@@ -97,14 +97,36 @@ __device__ __forceinline__ float row_group_max(float m, float* red) {
 // scalar loads, and the row is read a second time (it is still in L2).
 // grid = (ceil(R / (256 / TPR)), batch)
 // ---------------------------------------------------------------------------------------------
+// One k-contiguous operand of a split launch.
+struct KmajorOperand {
+    const float* src;
+    const float* given_max;     // externally reduced row maxima, or null
+    int8_t* planes;
+    int* expo;
+    int R;
+    long long batch_stride;
+};
+
+// The kernel takes up to two operands of the same row length (op(A) and op(B)^T of one product when
+// both are stored k-contiguous): blocks [0, blocks_first) work on `first`, the rest on `second`, so
+// the forward GEMM of a linear layer needs one pre-pass launch.  `zero_word`, if not null, is cleared
+// by one thread (the workspace's status word, when no memset precedes this launch).
 template <int S, int TPR, int CHUNKS, bool VEC>
 __global__ void __launch_bounds__(PREPASS_THREADS)
-split_kmajor_kernel(const float* __restrict__ src, const float* __restrict__ given_max,
-                    int8_t* __restrict__ planes, int* __restrict__ expo,
-                    int R, int K, int Kp, long long src_batch_stride) {
+split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int blocks_first,
+                    int K, int Kp, int* zero_word) {
     __shared__ float red[PREPASS_THREADS / 32];
     constexpr int rows_per_cta = PREPASS_THREADS / TPR;
-    const int row = blockIdx.x * rows_per_cta + threadIdx.x / TPR;
+    if (zero_word && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *zero_word = 0;
+    const bool is_first = (int)blockIdx.x < blocks_first;
+    const KmajorOperand& op = is_first ? first : second;
+    const float* __restrict__ src = op.src;
+    const float* __restrict__ given_max = op.given_max;
+    int8_t* __restrict__ planes = op.planes;
+    int* __restrict__ expo = op.expo;
+    const int R = op.R;
+    const long long src_batch_stride = op.batch_stride;
+    const int row = ((int)blockIdx.x - (is_first ? 0 : blocks_first)) * rows_per_cta + threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
     const int b = blockIdx.y;
     const bool live = row < R;
