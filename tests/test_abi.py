@@ -142,3 +142,45 @@ def test_plan_without_a_device_fails_cleanly(L):
     assert rc != 0 and plan is None
     rc, _ = rg.make_plan(64, 64, 64, rg.Config(algo=rg.Algo.Tiled))
     assert rc == rg.cudaErrorNotSupported
+
+
+CXX_CALLER = r"""
+// A caller written against the reference's C++ surface (repro_gemm_cuda/repro_gemm.cuh:25-75).
+#include "repro_gemm.cuh"
+#include <cstdio>
+int main() {
+    repro_gemm::Config cfg;                       // the reference's defaults
+    cfg.slices = 2;
+    cfg.trans_b = true;
+    repro_gemm::Plan plan{};
+    cudaError_t e = repro_gemm::make_plan(128, 64, 256, cfg, &plan);
+    cudaError_t bad = repro_gemm::make_plan(128, 64, 256, cfg, nullptr);
+    cfg.algo = repro_gemm::Algo::Tiled;
+    cudaError_t tiled = repro_gemm::make_plan(128, 64, 256, cfg, &plan);
+    std::printf("%d %d %d %s %s %d\n", (int)e, (int)bad, (int)tiled, repro_gemm::algo_name(repro_gemm::Algo::TensorCore),
+                repro_gemm::algo_name(repro_gemm::Algo::Reference), repro_gemm::MAX_SLICES);
+    return 0;
+}
+"""
+
+
+def test_cxx_caller_builds_against_the_shim_and_links_the_library(L, tmp_path):
+    """A C++ program using the reference's namespace, types and defaults compiles against
+    include/repro_gemm.cuh and links librgb200.so; without a GPU the calls fail cleanly."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    src = tmp_path / "caller.cu"
+    src.write_text(CXX_CALLER)
+    exe = tmp_path / "caller"
+    libdir = os.path.dirname(build.LIB)
+    subprocess.run([nvcc, "-std=c++17", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src),
+                    "-L", libdir, "-lrgb200", "-Xlinker", "-rpath", "-Xlinker", libdir], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    import torch
+    if not torch.cuda.is_available():
+        assert int(out[0]) != 0                    # no device: an error code, not a crash
+    assert int(out[1]) == rg.cudaErrorInvalidValue and int(out[2]) == rg.cudaErrorNotSupported
+    assert out[3:] == ["tc", "ref", "3"]
