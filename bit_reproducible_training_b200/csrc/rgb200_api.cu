@@ -322,29 +322,29 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         launch_kmajor<S>(opa, opb, L.K, L.Kp, L.batch, status, a.st);
         record(1);
     } else {
-    e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
-    if (e != cudaSuccess) return e;
-    record(0);
-    // The two operands are independent until the MMA kernel.  For large operands A's split runs on a side
-    // stream next to B's (fork and join by events, so the caller's stream still orders everything; this
-    // also holds inside a stream capture).  cudaStreamWaitEvent binds to the record made just before it,
-    // and the mutex keeps another host thread from re-recording the shared event in between.
-    const bool fork = dev.side != nullptr && (double)L.batch * L.K * ((double)L.M + L.N) >= 8.0e6;
-    bool forked = false;
-    if (fork) {
-        std::lock_guard<std::mutex> lock(dev.fork_mutex);
-        forked = cudaEventRecord(dev.fork_ev, a.st) == cudaSuccess &&
-                 cudaStreamWaitEvent(dev.side, dev.fork_ev, 0) == cudaSuccess;
-        if (!forked) (void)cudaGetLastError();
-    }
-    launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, forked ? dev.side : a.st);
-    launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, a.st);
-    if (forked) {
-        std::lock_guard<std::mutex> lock(dev.fork_mutex);
-        if (cudaEventRecord(dev.join_ev, dev.side) != cudaSuccess || cudaStreamWaitEvent(a.st, dev.join_ev, 0) != cudaSuccess)
-            return cudaErrorUnknown;          // the side stream could not be joined: do not run on half-ordered data
-    }
-    record(1);
+        e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
+        if (e != cudaSuccess) return e;
+        record(0);
+        // The two operands are independent until the MMA kernel.  For large operands A's split runs on a side
+        // stream next to B's (fork and join by events, so the caller's stream still orders everything; this
+        // also holds inside a stream capture).  cudaStreamWaitEvent binds to the record made just before it,
+        // and the mutex keeps another host thread from re-recording the shared event in between.
+        const bool fork = dev.side != nullptr && (double)L.batch * L.K * ((double)L.M + L.N) >= 8.0e6;
+        bool forked = false;
+        if (fork) {
+            std::lock_guard<std::mutex> lock(dev.fork_mutex);
+            forked = cudaEventRecord(dev.fork_ev, a.st) == cudaSuccess &&
+                     cudaStreamWaitEvent(dev.side, dev.fork_ev, 0) == cudaSuccess;
+            if (!forked) (void)cudaGetLastError();
+        }
+        launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, forked ? dev.side : a.st);
+        launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, a.st);
+        if (forked) {
+            std::lock_guard<std::mutex> lock(dev.fork_mutex);
+            if (cudaEventRecord(dev.join_ev, dev.side) != cudaSuccess || cudaStreamWaitEvent(a.st, dev.join_ev, 0) != cudaSuccess)
+                return cudaErrorUnknown;          // the side stream could not be joined: do not run on half-ordered data
+        }
+        record(1);
     }
 
     if (L.algo == RGB200_ALGO_REFERENCE) {
