@@ -214,14 +214,17 @@ class HostGemm:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.block = M if self.cfg.trans_a else max(1, min(block_rows, M))
         self.blocks = [(lo, min(M, lo + self.block)) for lo in range(0, M, self.block)]
-        rc, plan = make_plan(self.block, N, K, self.cfg)
-        if rc != cudaSuccess:
-            raise ReproGemmError(rc, "make_plan")
+        ws_bytes = 0
+        for rows in {hi - lo for lo, hi in self.blocks}:       # a short last block may plan K ranges of its own
+            rc, plan = make_plan(rows, N, K, self.cfg)
+            if rc != cudaSuccess:
+                raise ReproGemmError(rc, "make_plan")
+            ws_bytes = max(ws_bytes, plan.workspace_bytes)
         with torch.cuda.device(self.device):
             self.dA = torch.empty(M * K, dtype=torch.float32, device=self.device)
             self.dB = torch.empty(K * N, dtype=torch.float32, device=self.device)
             self.dC = torch.empty(M * N, dtype=torch.float32, device=self.device)
-            self.ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=self.device)
+            self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
             self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
             self.ev_b = torch.cuda.Event()
             self.ev_a = [torch.cuda.Event() for _ in self.blocks]
