@@ -259,6 +259,21 @@ def test_host_buffer_pipeline_matches_single_call():
     assert len(pipe.blocks) == 1 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
 
 
+def test_host_buffer_pipeline_short_last_block_with_own_k_ranges():
+    """A short last block can plan K ranges (few tiles) and then needs more workspace than the full
+    blocks do: the pipeline sizes its workspace for every block height."""
+    M, N, K = 512 + 128, 2432, 4096
+    assert rg.make_plan(512, N, K, rg.Config())[1].split_k == 1 and rg.make_plan(128, N, K, rg.Config())[1].split_k > 1
+    g = fx.Rng(77)
+    A, B = g.normal(M * K), g.normal(K * N)
+    want = rg.gemm(dev(A), dev(B), M, N, K).cpu().numpy()
+    hA, hB, hC = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory(), torch.empty(M * N).pin_memory()
+    pipe = rg.HostGemm(M, N, K, rg.Config(), block_rows=512)
+    pipe(hA, hB, hC)
+    torch.cuda.synchronize()
+    assert len(pipe.blocks) == 2 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
+
+
 def test_bounded_wait_expires_and_reports():
     """Failure detection without a fault: a wait that nothing will satisfy runs into its (short) limit,
     leaves a status code, makes the other waiting role leave too, and the device keeps working."""
