@@ -348,7 +348,7 @@ def main():
                 "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 4,
                         "d2h_bytes_per_step": M * N * 4},
                 "gpu_launches": (4 if ks is None else ks.launches_per_step) * args.steps,
-                "e2e_gpu_launches": 4 * len(host_gemm.blocks) * args.steps}
+                "e2e_gpu_launches": (4 * len(host_gemm.blocks) + host_gemm.blocks_with_k_ranges) * args.steps}
         if stages:
             mma_ops = 2.0 * S * S * M * N * K
             achieved = mma_ops / (stages["mma_ms"] * 1e-3) / 1e12

@@ -214,12 +214,14 @@ class HostGemm:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.block = M if self.cfg.trans_a else max(1, min(block_rows, M))
         self.blocks = [(lo, min(M, lo + self.block)) for lo in range(0, M, self.block)]
-        ws_bytes = 0
-        for rows in {hi - lo for lo, hi in self.blocks}:       # a short last block may plan K ranges of its own
+        ws_bytes, self.blocks_with_k_ranges = 0, 0
+        for rows in {hi - lo for lo, hi in self.blocks}:       # a short block may plan K ranges of its own
             rc, plan = make_plan(rows, N, K, self.cfg)
             if rc != cudaSuccess:
                 raise ReproGemmError(rc, "make_plan")
             ws_bytes = max(ws_bytes, plan.workspace_bytes)
+            if plan.split_k > 1:                               # those blocks launch one more kernel (the reduction)
+                self.blocks_with_k_ranges += sum(1 for lo, hi in self.blocks if hi - lo == rows)
         with torch.cuda.device(self.device):
             self.dA = torch.empty(M * K, dtype=torch.float32, device=self.device)
             self.dB = torch.empty(K * N, dtype=torch.float32, device=self.device)

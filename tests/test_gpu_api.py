@@ -271,7 +271,7 @@ def test_host_buffer_pipeline_short_last_block_with_own_k_ranges():
     pipe = rg.HostGemm(M, N, K, rg.Config(), block_rows=512)
     pipe(hA, hB, hC)
     torch.cuda.synchronize()
-    assert len(pipe.blocks) == 2 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
+    assert len(pipe.blocks) == 2 and pipe.blocks_with_k_ranges == 1 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
 
 
 def test_bounded_wait_expires_and_reports():
