@@ -20,6 +20,10 @@ class LayoutInfo(C.Structure):
                 ("partial_bytes", C.c_size_t), ("workspace_bytes", C.c_size_t)]
 
 
+class ConvShape(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("N", "C", "H", "W", "F", "KH", "KW", "SY", "SX", "PY", "PX")]
+
+
 _lib = None
 
 
@@ -63,5 +67,9 @@ def lib():
     L.rgb200_round_to_float_bits.argtypes = [ll, i]
     L.rgb200_round_to_float_bits.restype = C.c_uint32
     L.rgb200_layout.argtypes = [i, i, i, i, cfgp, C.POINTER(LayoutInfo)]
+    shp = C.POINTER(ConvShape)
+    for name in ("rgb200_conv2d", "rgb200_conv2d_grad_weight", "rgb200_conv2d_grad_input"):
+        getattr(L, name + "_workspace").argtypes = [shp, i, C.POINTER(C.c_size_t)]
+        getattr(L, name + "_ws").argtypes = [fp, fp, fp, shp, i, vp, C.c_size_t, vp]
     _lib = L
     return L

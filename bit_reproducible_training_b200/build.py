@@ -14,8 +14,9 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "librgb200.so")
 SOURCES = ["rgb200_api.cu", "rgb200_cxx.cu"]
-HEADERS = ["rgb200_math.cuh", "rgb200_mma.cuh", "rgb200_prepass.cuh", os.path.join("..", "..", "include", "rgb200.h"),
-           os.path.join("..", "..", "include", "repro_gemm.cuh")]
+HEADERS = ["rgb200_math.cuh", "rgb200_mma.cuh", "rgb200_prepass.cuh", "rgb200_conv.cuh",
+           os.path.join("..", "..", "include", "rgb200.h"), os.path.join("..", "..", "include", "repro_gemm.cuh"),
+           os.path.join("..", "..", "include", "repro_conv.cuh")]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--fmad=false",
               "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]

@@ -14,6 +14,7 @@
 #include "rgb200_math.cuh"
 #include "rgb200_mma.cuh"
 #include "rgb200_prepass.cuh"
+#include "rgb200_conv.cuh"
 
 namespace rgb200 {
 namespace {
@@ -72,14 +73,15 @@ int auto_split(int M, int N, int batch, int k_blocks, int tile_n) {
     return best;
 }
 
+// sum_limit bounds total_k * max|X|^2, the largest magnitude an exact sum can reach.
 cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const rgb200_config& cfg,
-                        bool partial_out, Layout& L) {
+                        bool partial_out, Layout& L, double sum_limit = 4611686018427387904.0 /* 2^62 */) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || cfg.split_k <= 0 || total_k < K) return cudaErrorInvalidValue;
     if (cfg.slices < 1 || cfg.slices > 3) return cudaErrorInvalidValue;
     if (cfg.algo < RGB200_ALGO_AUTO || cfg.algo > RGB200_ALGO_TENSORCORE) return cudaErrorInvalidValue;
     const int S = cfg.slices;
     const double d = max_fixed_point(S);
-    if ((double)total_k * d * d > std::ldexp(1.0, 62)) return cudaErrorInvalidValue;   // INT64 must hold any sum
+    if ((double)total_k * d * d > sum_limit) return cudaErrorInvalidValue;   // INT64 must hold any sum
     if ((long long)K + BLOCK_K > 0x7FFFFFFFll) return cudaErrorInvalidValue;
     // launch-geometry limits: the batch index is a grid y/z coordinate, row counts times batch are 32-bit
     if (batch > 65535 || (long long)batch * (M > N ? M : N) > 0x7FFFFFFFll) return cudaErrorInvalidValue;
@@ -284,6 +286,15 @@ void launch_round(const long long* partial, int parts, size_t part_stride, const
     else round_partial_kernel<false><<<blocks, 256, 0, st>>>(partial, parts, part_stride, ea, eb, max_a, max_b, C, M, N, batch, stride_c, e0);
 }
 
+// A pre-pass supplied by the caller of run(): fills both operands' digit planes and exponents
+// (the convolutions read their operands through index maps instead of stored matrices).
+// max_a / max_b are zeroed scratch words, batch * M and batch * N of them.
+struct PrepassHook {
+    cudaError_t (*launch)(const void* ctx, const Layout& L, uint32_t* max_a, uint32_t* max_b, int8_t* qa, int8_t* qb,
+                          int* ea, int* eb, cudaStream_t st);
+    const void* ctx;
+};
+
 struct RunArgs {
     const float *A, *B;
     float* C;
@@ -296,6 +307,7 @@ struct RunArgs {
     const cudaEvent_t* ev;
     long long* const* scatter = nullptr;   // per-owner destination buffers of the INT64 sums (K-sharded), or null
     int scatter_world = 0, scatter_rank = 0;
+    const PrepassHook* hook = nullptr;
 };
 
 template <int S>
@@ -315,7 +327,13 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     // Both operands k-contiguous (the forward product of a linear layer, C = A B^T): one launch splits both
     // and clears the status word; no column maxima are needed, hence no memset either.
     const bool both_kmajor = !a.trans_a && a.trans_b;
-    if (both_kmajor) {
+    if (a.hook) {
+        e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);
+        if (e != cudaSuccess) return e;
+        record(0);
+        if ((e = a.hook->launch(a.hook->ctx, L, max_a, max_b, qa, qb, ea, eb, a.st)) != cudaSuccess) return e;
+        record(1);
+    } else if (both_kmajor) {
         record(0);
         const KmajorOperand opa{a.A, a.max_a, qa, ea, L.M, a.stride_a};
         const KmajorOperand opb{a.B, a.max_b, qb, eb, L.N, a.stride_b};
@@ -418,6 +436,115 @@ cudaError_t gemm_ws(const float* A, const float* B, float* C, int M, int N, int 
     if (batch > 1 && (sa < (long long)M * K || sb < (long long)K * N || sc < (long long)M * N)) return cudaErrorInvalidValue;
     RunArgs a{A, B, C, nullptr, nullptr, nullptr, sa, sb, sc, cfg->trans_a != 0, cfg->trans_b != 0,
               static_cast<char*>(ws), static_cast<cudaStream_t>(stream), reinterpret_cast<const cudaEvent_t*>(events4)};
+    return dispatch(L, a, *dev);
+}
+
+
+// ------------------------------------------------------------------------------------------
+// Convolutions (reference: repro_conv_cuda/repro_conv.cu:157-238).  Each call is one (batched)
+// product on digit planes that a gather pre-pass writes; see rgb200_conv.cuh for the mapping.
+// ------------------------------------------------------------------------------------------
+enum ConvKind { CONV_FORWARD, CONV_GRAD_WEIGHT, CONV_GRAD_INPUT };
+
+// The reference's shape check (repro_conv.cu:157-167) without its kernel-specific limits on the
+// window size (1024) and the filter count (256), which this implementation does not have.
+bool conv_geometry(const rgb200_conv_shape* s, int S, ConvGeom& g) {
+    if (!s || S < 1 || S > 3) return false;
+    if (s->N <= 0 || s->C <= 0 || s->H <= 0 || s->W <= 0 || s->F <= 0 || s->KH <= 0 || s->KW <= 0) return false;
+    if (s->SY <= 0 || s->SX <= 0 || s->PY < 0 || s->PX < 0) return false;
+    if ((long long)s->H + 2ll * s->PY < s->KH || (long long)s->W + 2ll * s->PX < s->KW) return false;
+    if (s->N > 65535) return false;
+    const long long OH = ((long long)s->H + 2ll * s->PY - s->KH) / s->SY + 1, OW = ((long long)s->W + 2ll * s->PX - s->KW) / s->SX + 1;
+    const double K = (double)s->C * s->KH * s->KW, windows = (double)s->N * OH * OW;
+    const double out_size = windows * s->F, in_size = (double)s->N * s->C * s->H * s->W;
+    if (out_size >= 2147483648.0 || in_size >= 2147483648.0 || K * s->F >= 2147483648.0) return false;
+    const double lim = 127.0 * (double)(1 << (7 * (S - 1))), max_terms = 9.0e18 / (lim * lim);   // keeps |sum| < 2^63
+    if (windows > max_terms || (double)s->KH * s->KW * s->F > max_terms || K > max_terms) return false;
+    g.N = s->N; g.C = s->C; g.H = s->H; g.W = s->W; g.F = s->F; g.KH = s->KH; g.KW = s->KW;
+    g.SY = s->SY; g.SX = s->SX; g.PY = s->PY; g.PX = s->PX;
+    g.OH = (int)OH; g.OW = (int)OW; g.K = s->C * s->KH * s->KW;
+    return true;
+}
+
+cudaError_t conv_layout(ConvKind kind, const ConvGeom& g, int S, Layout& L) {
+    rgb200_config cfg;
+    rgb200_default_config(&cfg);
+    cfg.slices = S;
+    cfg.algo = RGB200_ALGO_TENSORCORE;
+    const double no_limit = 1.0e300;             // conv_geometry has bounded the sums already
+    switch (kind) {
+        case CONV_FORWARD: return plan_layout(g.F, g.OH * g.OW, g.K, g.K, g.N, cfg, false, L, no_limit);
+        case CONV_GRAD_WEIGHT: { const int w = g.N * g.OH * g.OW; return plan_layout(g.F, g.K, w, w, 1, cfg, false, L, no_limit); }
+        case CONV_GRAD_INPUT: { const int t = g.F * g.KH * g.KW; return plan_layout(g.C, g.H * g.W, t, t, g.N, cfg, false, L, no_limit); }
+    }
+    return cudaErrorInvalidValue;
+}
+
+struct ConvCall { ConvKind kind; ConvGeom g; const float* p; const float* q; };   // (x, weight), (dy, x) or (dy, weight)
+
+cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint32_t* max_b, int8_t* qa, int8_t* qb,
+                         int* ea, int* eb, cudaStream_t st) {
+    const ConvCall& c = *static_cast<const ConvCall*>(ctx);
+    const ConvGeom& g = c.g;
+    const int S = L.S;
+    switch (c.kind) {
+        case CONV_FORWARD: {          // A: the weights as stored, one copy of the planes per image; B: windows of image b
+            const StoredRows w{c.q, g.K};
+            launch_gather_max(w, max_a, L.M, L.K, 1, 0, 1, st);
+            launch_gather_split(S, w, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 1, st);   // every image reads the same filter maxima
+            const WindowsOfImage x{c.p, g};
+            launch_gather_max(x, max_b, L.N, L.K, L.batch, L.N, 1, st);
+            launch_gather_split(S, x, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, L.N, 1, st);
+            break;
+        }
+        case CONV_GRAD_WEIGHT: {      // A: dY by filter over all windows; B: window values by position over all windows
+            const FiltersOverWindows d{c.p, g};
+            launch_gather_max(d, max_a, L.M, L.K, 1, 0, 1, st);
+            launch_gather_split(S, d, max_a, qa, ea, L.M, L.K, L.Kp, 1, 0, 1, st);
+            const PositionsOverWindows x{c.q, g};
+            launch_gather_max(x, max_b, L.N, L.K, 1, 0, 1, st);
+            launch_gather_split(S, x, max_b, qb, eb, L.N, L.K, L.Kp, 1, 0, 1, st);
+            break;
+        }
+        case CONV_GRAD_INPUT: {       // A: weights by input channel, one scale for all; B: dY taps per pixel, one scale per image
+            const StoredRows all_w{c.q, (long long)g.F * g.K};
+            launch_gather_max(all_w, max_a, 1, g.F * g.K, 1, 0, 0, st);
+            const ChannelsOverTaps w{c.q, g};
+            launch_gather_split(S, w, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 0, st);
+            const StoredRows images{c.p, (long long)g.F * g.OH * g.OW};
+            launch_gather_max(images, max_b, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
+            const PixelsOverTaps d{c.p, g};
+            launch_gather_split(S, d, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, 1, 0, st);
+            break;
+        }
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t conv_workspace(ConvKind kind, const rgb200_conv_shape* shape, int S, size_t* bytes) {
+    ConvGeom g;
+    if (!bytes || !conv_geometry(shape, S, g)) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = conv_layout(kind, g, S, L);
+    if (e == cudaSuccess) *bytes = L.total;
+    return e;
+}
+
+cudaError_t conv_run(ConvKind kind, const float* p, const float* q, float* out, const rgb200_conv_shape* shape, int S,
+                     void* ws, size_t ws_bytes, void* stream) {
+    ConvGeom g;
+    if (!conv_geometry(shape, S, g)) return cudaErrorInvalidValue;
+    Layout L;
+    cudaError_t e = conv_layout(kind, g, S, L);
+    if (e != cudaSuccess) return e;
+    if (!p || !q || !out || !ws || ws_bytes < L.total) return cudaErrorInvalidValue;
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
+    const ConvCall call{kind, g, p, q};
+    const PrepassHook hook{conv_prepass, &call};
+    RunArgs a{nullptr, nullptr, out, nullptr, nullptr, nullptr, 0, 0, (long long)L.M * L.N, false, true,
+              static_cast<char*>(ws), static_cast<cudaStream_t>(stream), nullptr};
+    a.hook = &hook;
     return dispatch(L, a, *dev);
 }
 
@@ -525,6 +652,28 @@ int rgb200_make_plan_partial(int M, int N, int K, long long total_k, const rgb20
 int rgb200_gemm_fp32_ws(const float* A, const float* B, float* C, int M, int N, int K, const rgb200_config* cfg,
                         void* workspace, size_t workspace_bytes, void* stream, void* const* events4) {
     return gemm_ws(A, B, C, M, N, K, 1, 0, 0, 0, cfg, workspace, workspace_bytes, stream, events4);
+}
+
+int rgb200_conv2d_workspace(const rgb200_conv_shape* shape, int slices, size_t* bytes) {
+    return conv_workspace(CONV_FORWARD, shape, slices, bytes);
+}
+int rgb200_conv2d_grad_weight_workspace(const rgb200_conv_shape* shape, int slices, size_t* bytes) {
+    return conv_workspace(CONV_GRAD_WEIGHT, shape, slices, bytes);
+}
+int rgb200_conv2d_grad_input_workspace(const rgb200_conv_shape* shape, int slices, size_t* bytes) {
+    return conv_workspace(CONV_GRAD_INPUT, shape, slices, bytes);
+}
+int rgb200_conv2d_ws(const float* x, const float* weight, float* out, const rgb200_conv_shape* shape, int slices,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    return conv_run(CONV_FORWARD, x, weight, out, shape, slices, workspace, workspace_bytes, stream);
+}
+int rgb200_conv2d_grad_weight_ws(const float* dy, const float* x, float* dw, const rgb200_conv_shape* shape, int slices,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+    return conv_run(CONV_GRAD_WEIGHT, dy, x, dw, shape, slices, workspace, workspace_bytes, stream);
+}
+int rgb200_conv2d_grad_input_ws(const float* dy, const float* weight, float* dx, const rgb200_conv_shape* shape, int slices,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+    return conv_run(CONV_GRAD_INPUT, dy, weight, dx, shape, slices, workspace, workspace_bytes, stream);
 }
 
 int rgb200_gemm_fp32_batched_ws(const float* A, const float* B, float* C, int M, int N, int K, int batch,

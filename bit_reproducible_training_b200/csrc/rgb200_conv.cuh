@@ -1,0 +1,166 @@
+// Convolution as an implicit GEMM: the scale-and-split pre-pass reads the image (or the output
+// gradient) through an index map instead of a stored im2col matrix, writes the same int8 digit
+// planes the matrix pre-pass writes, and the tcgen05 kernel runs unchanged on them.
+//
+// Definition (reference: repro_conv_cuda/repro_conv_math.cuh:1-22, repro_conv_cpu.h:25-90), with
+// a "window" one (n, oy, ox), position k = (c, ky, kx), K = C*KH*KW and e0 = -14 (S - 1):
+//   forward      Y[n, f, oy, ox] = round(sum_k X[w, k] W[f, k],  e_window(w) + e_filter(f) + e0)
+//   weight grad  dW[f, k]        = round(sum_w D[w, f] X[w, k],  e_filter(dY, f) + e_position(k) + e0)
+//   input grad   dX[n, c, y, x]  = round(sum D[w, f] W[f, k],    e_image(dY, n) + e_all_weights + e0)
+// The first two are the GEMM definition applied to the im2col matrix; the third is a GEMM over
+// k = (f, ky, kx) whose operands use one scale per image and one for all weights.
+//
+// As products on the digit planes (rows of op(A) x rows of op(B)^T, k contiguous in both):
+//   forward      per image n:  [F x K] weights          times  [OH*OW x K] windows of image n
+//   weight grad  one product:  [F x windows] dY          times  [K x windows] window values
+//   input grad   per image n:  [C x F*KH*KW] weights     times  [H*W x F*KH*KW] dY taps of image n
+// so every result lands directly in the PyTorch layout of its tensor.
+#pragma once
+#include "rgb200_prepass.cuh"
+
+namespace rgb200 {
+
+struct ConvGeom {
+    int N, C, H, W, F, KH, KW, SY, SX, PY, PX;
+    int OH, OW, K;            // output height and width, values per window
+};
+
+// ---------------------------------------------------------------------------------------------
+// Index maps: at(b, r, k) is element (row r, index k) of operand matrix number b.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float conv_window_value(const float* __restrict__ x, const ConvGeom& g, int n, int oy, int ox, int k) {
+    const int khw = g.KH * g.KW;
+    const int c = k / khw, rem = k - c * khw;
+    const int ky = rem / g.KW, kx = rem - ky * g.KW;
+    const int y = oy * g.SY - g.PY + ky, xx = ox * g.SX - g.PX + kx;
+    if ((unsigned)y >= (unsigned)g.H || (unsigned)xx >= (unsigned)g.W) return 0.0f;   // zero padding
+    return __ldg(x + (((size_t)n * g.C + c) * g.H + y) * g.W + xx);
+}
+
+struct WindowsOfImage {      // forward: b = image, r = window (oy, ox) of that image, k = position
+    const float* x; ConvGeom g;
+    __device__ __forceinline__ float at(int b, int r, int k) const {
+        const int oy = r / g.OW;
+        return conv_window_value(x, g, b, oy, r - oy * g.OW, k);
+    }
+};
+
+struct PositionsOverWindows {   // weight gradient: r = position, k = window (n, oy, ox)
+    const float* x; ConvGeom g;
+    __device__ __forceinline__ float at(int, int r, int k) const {
+        const int per = g.OH * g.OW;
+        const int n = k / per, j = k - n * per;
+        const int oy = j / g.OW;
+        return conv_window_value(x, g, n, oy, j - oy * g.OW, r);
+    }
+};
+
+struct FiltersOverWindows {     // weight gradient: r = filter, k = window (n, oy, ox); dY is [N][F][OH*OW]
+    const float* dy; ConvGeom g;
+    __device__ __forceinline__ float at(int, int r, int k) const {
+        const int per = g.OH * g.OW;
+        const int n = k / per, j = k - n * per;
+        return __ldg(dy + ((size_t)n * g.F + r) * per + j);
+    }
+};
+
+struct ChannelsOverTaps {       // input gradient: r = input channel, k = (f, ky, kx); weights are [F][C][KH][KW]
+    const float* w; ConvGeom g;
+    __device__ __forceinline__ float at(int, int r, int k) const {
+        const int khw = g.KH * g.KW;
+        const int f = k / khw, rem = k - f * khw;
+        return __ldg(w + ((size_t)f * g.C + r) * khw + rem);
+    }
+};
+
+struct PixelsOverTaps {         // input gradient: b = image, r = pixel (y, x), k = (f, ky, kx)
+    const float* dy; ConvGeom g;
+    __device__ __forceinline__ float at(int b, int r, int k) const {
+        const int khw = g.KH * g.KW;
+        const int f = k / khw, rem = k - f * khw;
+        const int ky = rem / g.KW, kx = rem - ky * g.KW;
+        const int y = r / g.W, xx = r - y * g.W;
+        // the window whose tap (ky, kx) lies on this pixel, if the strides allow one
+        const int ry = y + g.PY - ky, rx = xx + g.PX - kx;
+        if (ry < 0 || rx < 0) return 0.0f;
+        const int oy = ry / g.SY, ox = rx / g.SX;
+        if (oy * g.SY != ry || ox * g.SX != rx || oy >= g.OH || ox >= g.OW) return 0.0f;
+        return __ldg(dy + (((size_t)b * g.F + f) * g.OH + oy) * g.OW + ox);
+    }
+};
+
+struct StoredRows {             // a stored matrix [R][K]: used for the maxima of whole tensors
+    const float* src; long long row_len;
+    __device__ __forceinline__ float at(int, int r, int k) const { return __ldg(src + (size_t)r * row_len + k); }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Pre-pass over an index map, two launches of the same shape: maxima (integer atomicMax on the bit
+// patterns, exact and order-free; the slots must be zero on entry), then scale and split.
+// One warp works on one row and one chunk of GATHER_CHUNK indices, so short rows (a window) and
+// long rows (all windows of a position) both spread over the GPU.
+// A row's maximum lives in maxbits[b * slot_batch_mul + r * slot_row_mul]: (R, 1) gives one scale per
+// row, (1, 0) one per operand matrix, (0, 0) one for everything.
+// grid = (ceil(R / 8), ceil(K or Kp / GATHER_CHUNK), batch), 256 threads
+// ---------------------------------------------------------------------------------------------
+constexpr int GATHER_CHUNK = 1024;
+
+template <class Source>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+gather_max_kernel(const Source src, uint32_t* __restrict__ maxbits, int R, int K, int slot_batch_mul, int slot_row_mul) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5);
+    const int b = blockIdx.z;
+    if (row >= R) return;
+    const int k_lo = blockIdx.y * GATHER_CHUNK, k_hi = min(K, k_lo + GATHER_CHUNK);
+    float m = 0.0f;
+    for (int k = k_lo + lane; k < k_hi; k += 32) m = fmaxf(m, fabsf(src.at(b, row, k)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane == 0 && m > 0.0f) atomicMax(maxbits + (size_t)b * slot_batch_mul + (size_t)row * slot_row_mul, f32_bits(m));
+}
+
+template <int S, class Source>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+gather_split_kernel(const Source src, const uint32_t* __restrict__ maxbits, int8_t* __restrict__ planes,
+                    int* __restrict__ expo, int R, int K, int Kp, int slot_batch_mul, int slot_row_mul) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5);
+    const int b = blockIdx.z;
+    if (row >= R) return;
+    const int e = scale_exponent(bits_f32(maxbits[(size_t)b * slot_batch_mul + (size_t)row * slot_row_mul]));
+    if (blockIdx.y == 0 && lane == 0) expo[(size_t)b * R + row] = e;
+    const QuantScale q = quant_scale(e, S);
+    const bool plain = plain_row(e);
+    const size_t plane_stride = (size_t)R * Kp;
+    int8_t* out = planes + (size_t)b * S * plane_stride + (size_t)row * Kp;
+    const int k_lo = blockIdx.y * GATHER_CHUNK, k_hi = min(Kp, k_lo + GATHER_CHUNK);
+    for (int k = k_lo + lane * 4; k < k_hi; k += 128) {          // a warp writes 128 contiguous bytes per plane
+        float4 v;
+        v.x = k + 0 < K ? src.at(b, row, k + 0) : 0.0f;          // k >= K: the zero padding up to Kp
+        v.y = k + 1 < K ? src.at(b, row, k + 1) : 0.0f;
+        v.z = k + 2 < K ? src.at(b, row, k + 2) : 0.0f;
+        v.w = k + 3 < K ? src.at(b, row, k + 3) : 0.0f;
+        store_quad<S>(v, q, plain, out, plane_stride, (size_t)k);
+    }
+}
+
+template <class Source>
+void launch_gather_max(const Source& src, uint32_t* maxbits, int R, int K, int batch, int slot_batch_mul, int slot_row_mul,
+                       cudaStream_t st) {
+    const dim3 grid((R + 7) / 8, (K + GATHER_CHUNK - 1) / GATHER_CHUNK, batch);
+    gather_max_kernel<Source><<<grid, PREPASS_THREADS, 0, st>>>(src, maxbits, R, K, slot_batch_mul, slot_row_mul);
+}
+
+template <class Source>
+void launch_gather_split(int S, const Source& src, const uint32_t* maxbits, int8_t* planes, int* expo, int R, int K, int Kp,
+                         int batch, int slot_batch_mul, int slot_row_mul, cudaStream_t st) {
+    const dim3 grid((R + 7) / 8, (Kp + GATHER_CHUNK - 1) / GATHER_CHUNK, batch);
+    switch (S) {
+        case 1: gather_split_kernel<1, Source><<<grid, PREPASS_THREADS, 0, st>>>(src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul); break;
+        case 2: gather_split_kernel<2, Source><<<grid, PREPASS_THREADS, 0, st>>>(src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul); break;
+        default: gather_split_kernel<3, Source><<<grid, PREPASS_THREADS, 0, st>>>(src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul); break;
+    }
+}
+
+}  // namespace rgb200

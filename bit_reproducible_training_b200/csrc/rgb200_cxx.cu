@@ -38,3 +38,35 @@ cudaError_t repro_gemm_fp32(const float* A, const float* B, float* C, int M, int
 const char* algo_name(Algo a) { return rgb200_algo_name(static_cast<int>(a)); }
 
 }  // namespace repro_gemm
+
+// The convolution entry points with the reference's signatures (repro_conv_cuda/repro_conv.cuh:22-32).
+#include "../../include/repro_conv.cuh"
+
+namespace repro_conv {
+
+static_assert(sizeof(ConvShape) == sizeof(rgb200_conv_shape), "ConvShape and rgb200_conv_shape are the same eleven ints");
+static const rgb200_conv_shape* to_c(const ConvShape& g) { return reinterpret_cast<const rgb200_conv_shape*>(&g); }
+
+cudaError_t conv2d_workspace(const ConvShape& g, int S, size_t* bytes) {
+    return static_cast<cudaError_t>(rgb200_conv2d_workspace(to_c(g), S, bytes));
+}
+cudaError_t conv2d_grad_weight_workspace(const ConvShape& g, int S, size_t* bytes) {
+    return static_cast<cudaError_t>(rgb200_conv2d_grad_weight_workspace(to_c(g), S, bytes));
+}
+cudaError_t conv2d_grad_input_workspace(const ConvShape& g, int S, size_t* bytes) {
+    return static_cast<cudaError_t>(rgb200_conv2d_grad_input_workspace(to_c(g), S, bytes));
+}
+cudaError_t repro_conv2d_ws(const float* x, const float* weight, float* out, const ConvShape& g, int S,
+                            void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    return static_cast<cudaError_t>(rgb200_conv2d_ws(x, weight, out, to_c(g), S, workspace, workspace_bytes, stream));
+}
+cudaError_t repro_conv2d_grad_weight_ws(const float* dy, const float* x, float* dw, const ConvShape& g, int S,
+                                        void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    return static_cast<cudaError_t>(rgb200_conv2d_grad_weight_ws(dy, x, dw, to_c(g), S, workspace, workspace_bytes, stream));
+}
+cudaError_t repro_conv2d_grad_input_ws(const float* dy, const float* weight, float* dx, const ConvShape& g, int S,
+                                       void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    return static_cast<cudaError_t>(rgb200_conv2d_grad_input_ws(dy, weight, dx, to_c(g), S, workspace, workspace_bytes, stream));
+}
+
+}  // namespace repro_conv

@@ -252,3 +252,46 @@ def config5(batch=96, T=1024, HD=64):
     P = g.prob_rows(batch * T, T)
     return [dict(name="c5.QKt", batch=batch, M=T, N=T, K=HD, trans_a=False, trans_b=True, A=Q, B=Km),
             dict(name="c5.PV", batch=batch, M=T, N=HD, K=T, trans_a=False, trans_b=False, A=P, B=V)]
+
+
+# ------------------------------------------------------------------------------------------------
+# Convolution cases: shape = (N, C, H, W, F, KH, KW, SY, SX, PY, PX)
+# ------------------------------------------------------------------------------------------------
+CONV_CASES = [
+    # the six shapes of the reference's own GPU test (repro_conv_cuda/test_repro_conv.cu:126-131)
+    ("lenet1", (100, 1, 28, 28, 6, 5, 5, 1, 1, 2, 2), "normal"),
+    ("lenet2", (100, 6, 14, 14, 16, 5, 5, 1, 1, 0, 0), "normal"),
+    ("lenet1.small", (10, 1, 28, 28, 6, 5, 5, 1, 1, 2, 2), "normal"),
+    ("stride2.pad1", (4, 3, 17, 23, 8, 3, 5, 2, 2, 1, 1), "normal"),
+    ("stride3x1", (2, 2, 19, 11, 5, 4, 3, 3, 1, 0, 2), "normal"),
+    ("filters100", (2, 4, 12, 12, 100, 3, 3, 1, 1, 1, 1), "normal"),
+    # beyond the reference kernels' limits (more than 1024 values per window, more than 256 filters)
+    ("big.window", (2, 160, 9, 9, 40, 3, 3, 1, 1, 1, 1), "normal"),
+    ("many.filters", (1, 8, 10, 10, 300, 3, 3, 1, 1, 0, 0), "normal"),
+    # stride larger than the kernel (pixels no window touches), 1x1 kernel, one window, padding wider than the kernel
+    ("skipping", (3, 2, 13, 14, 7, 2, 2, 3, 4, 0, 0), "normal"),
+    ("pointwise", (2, 64, 7, 7, 96, 1, 1, 1, 1, 0, 0), "normal"),
+    ("one.window", (5, 3, 4, 6, 9, 4, 6, 1, 1, 0, 0), "normal"),
+    ("wide.padding", (2, 2, 5, 5, 4, 3, 3, 1, 1, 4, 5), "normal"),
+    # wide dynamic range with exact zeros and subnormals in every tensor
+    ("wide.range", (3, 5, 11, 9, 12, 3, 3, 1, 2, 1, 0), "wide"),
+    # enough windows that the weight gradient is cut into several accumulation ranges
+    ("many.windows", (64, 3, 48, 48, 8, 3, 3, 1, 1, 1, 1), "normal"),
+]
+
+
+def conv_output_dims(shape):
+    N, C, H, W, F, KH, KW, SY, SX, PY, PX = shape
+    return (H + 2 * PY - KH) // SY + 1, (W + 2 * PX - KW) // SX + 1
+
+
+def conv_inputs(shape, dist="normal", seed=2024):
+    """x, weight and dY for a convolution case, drawn in that order from one stream; magnitudes follow the
+    reference's test (repro_conv_cuda/test_repro_conv.cu:63-65): x ~ 1, weights ~ 0.1, dY ~ 1e-3."""
+    N, C, H, W, F, KH, KW, SY, SX, PY, PX = shape
+    oh, ow = conv_output_dims(shape)
+    g = Rng(seed)
+    sizes = (N * C * H * W, F * C * KH * KW, N * F * oh * ow)
+    if dist == "wide":
+        return tuple(g.wide_mixed(n) for n in sizes)
+    return g.normal(sizes[0]), g.normal(sizes[1], 0.1), g.normal(sizes[2], 1e-3)

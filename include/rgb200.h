@@ -167,6 +167,38 @@ int rgb200_selftest_bounded_wait(long long limit_clocks, int* status, long long*
 int rgb200_gemm_fp32_static(const float* A, const float* B, float* C, int M, int N, int K,
                             const rgb200_config* cfg, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * 2-D convolution and its two gradients in PyTorch layouts (x[N,C,H,W], weight[F,C,KH,KW], output and
+ * its gradient [N,F,OH,OW]), with stride and zero padding, no groups or dilation.  They replace
+ * repro_conv_cuda/repro_conv.cuh:22-32: conv2d_workspace, conv2d_grad_weight_workspace,
+ * conv2d_grad_input_workspace, repro_conv2d_ws, repro_conv2d_grad_weight_ws and
+ * repro_conv2d_grad_input_ws.  The shape struct has the field order of the reference's ConvShape
+ * (repro_conv_cuda/repro_conv_math.cuh:29-34); stride defaults there are 1, padding 0.
+ * Definition (repro_conv_math.cuh:10-17): forward and weight gradient are the GEMM definition applied
+ * to the im2col matrix (scales per window and per filter; per filter of dY and per window position);
+ * the input gradient uses one scale per image of dY and one for all weights.  No im2col matrix is
+ * stored: the pre-pass reads the tensors through an index map and the tensor-core kernel runs on the
+ * resulting digit planes.  Asynchronous on `stream`, allocation-free; the workspace size depends only
+ * on (shape, slices).  cudaErrorInvalidValue for unsupported shapes (the reference's checks,
+ * repro_conv.cu:157-167, except that windows may exceed 1024 values and filters 256) and for a null
+ * or short workspace.  Bias is not included (add it with one IEEE addition). */
+typedef struct rgb200_conv_shape {
+    int N, C, H, W;      /* input  [N, C, H, W] */
+    int F, KH, KW;       /* weight [F, C, KH, KW] */
+    int SY, SX;          /* stride (>= 1) */
+    int PY, PX;          /* zero padding (>= 0) */
+} rgb200_conv_shape;
+
+int rgb200_conv2d_workspace(const rgb200_conv_shape* shape, int slices, size_t* bytes);
+int rgb200_conv2d_grad_weight_workspace(const rgb200_conv_shape* shape, int slices, size_t* bytes);
+int rgb200_conv2d_grad_input_workspace(const rgb200_conv_shape* shape, int slices, size_t* bytes);
+int rgb200_conv2d_ws(const float* x, const float* weight, float* out, const rgb200_conv_shape* shape, int slices,
+                     void* workspace, size_t workspace_bytes, void* stream);
+int rgb200_conv2d_grad_weight_ws(const float* dy, const float* x, float* dw, const rgb200_conv_shape* shape, int slices,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+int rgb200_conv2d_grad_input_ws(const float* dy, const float* weight, float* dx, const rgb200_conv_shape* shape, int slices,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* Host-side helpers matching repro_gemm_cuda/repro_test_util.h:20-24 (FNV-1a-64 over raw bytes) and
  * repro_gemm_cuda/repro_gemm_math.cuh:59,74,96 (the three scalar functions, computed by this
  * library's own host code so callers can cross-check them without a GPU). */

@@ -15,6 +15,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "liboracle.so")
 _REF = os.path.join(_HERE, "_ref", "librepro_ref.so")
 _REF_CUDA = os.path.join(_HERE, "_ref", "librepro_ref_cuda.so")
+_REF_CONV = os.path.join(_HERE, "_ref", "librepro_ref_conv.so")
+REF_CONV_TEST_TOOL = os.path.join(_HERE, "_ref", "test_repro_conv_rgb200")
+REF_CONV_BENCH_TOOL = os.path.join(_HERE, "_ref", "bench_repro_conv_rgb200")
+REF_CONV_BENCH_REF = os.path.join(_HERE, "_ref", "bench_repro_conv_ref")
 REF_TEST_TOOL = os.path.join(_HERE, "_ref", "test_repro_gemm_rgb200")
 REF_HASH_TOOL = os.path.join(_HERE, "_ref", "hash_repro_gemm_rgb200")
 
@@ -25,9 +29,9 @@ def build(force=False):
     """Compile the checkers with oracle/Makefile (the reference build only where its sources exist)."""
     if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
         subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True, capture_output=True)
-    if force or not os.path.exists(_REF):
+    if force or not os.path.exists(_REF) or not os.path.exists(_REF_CONV):
         subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
-    if force or not os.path.exists(_REF_CUDA):
+    if force or not os.path.exists(_REF_CUDA) or not os.path.exists(REF_CONV_TEST_TOOL):
         subprocess.run(["make", "-C", _HERE, "ref_gpu"], check=True, capture_output=True)
 
 
@@ -58,6 +62,10 @@ def lib():
         L.orc_gemm_partial.restype = C.c_int
         L.orc_absmax.argtypes = [fp, fp, ip, ip, ip]
         L.orc_round_partials.argtypes = [i64p, ip, fp, fp, fp, ip, ip, ip]
+        ip11 = C.POINTER(C.c_int)
+        for name in ("orc_conv2d", "orc_conv2d_grad_weight", "orc_conv2d_grad_input"):
+            getattr(L, name).argtypes = [fp, fp, fp, ip11, ip, ip]
+            getattr(L, name).restype = C.c_int
         L.orc_fnv1a64.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64]
         L.orc_fnv1a64.restype = C.c_uint64
         st = C.POINTER(C.c_uint64)
@@ -155,6 +163,69 @@ def ref_gemm(A, B, M, N, K, ta=False, tb=False, S=3):
     out = np.empty((M, N), dtype=np.float32)
     R.ref_cpu_gemm(pa, pb, out.ctypes.data_as(C.POINTER(C.c_float)), M, N, K, int(ta), int(tb), S)
     return out
+
+
+# --- convolution: shape = (N, C, H, W, F, KH, KW, SY, SX, PY, PX) -----------------------------------
+def conv_dims(shape):
+    N, Cc, H, W, F, KH, KW, SY, SX, PY, PX = shape
+    return (H + 2 * PY - KH) // SY + 1, (W + 2 * PX - KW) // SX + 1
+
+
+def _conv_call(fn, a, b, out_shape, shape, S, threads=None):
+    a, pa = _f32(a)
+    b, pb = _f32(b)
+    out = np.empty(out_shape, dtype=np.float32)
+    arr = (C.c_int * 11)(*shape)
+    args = [pa, pb, out.ctypes.data_as(C.POINTER(C.c_float)), arr, S]
+    if threads is not False:
+        args.append(threads or default_threads())
+    rc = fn(*args)
+    if rc not in (0, None):
+        raise MemoryError("oracle convolution: allocation failed")
+    return out
+
+
+def conv2d(x, w, shape, S=3):
+    """out[N, F, OH, OW] by the restated definition."""
+    oh, ow = conv_dims(shape)
+    return _conv_call(lib().orc_conv2d, x, w, (shape[0], shape[4], oh, ow), shape, S)
+
+
+def conv2d_grad_weight(dy, x, shape, S=3):
+    return _conv_call(lib().orc_conv2d_grad_weight, dy, x, (shape[4], shape[1], shape[5], shape[6]), shape, S)
+
+
+def conv2d_grad_input(dy, w, shape, S=3):
+    return _conv_call(lib().orc_conv2d_grad_input, dy, w, shape[:4], shape, S)
+
+
+_ref_conv = None
+
+
+def ref_conv():
+    """The reference's own CPU convolutions, or None where they have not been built."""
+    global _ref_conv
+    if _ref_conv is None and os.path.exists(_REF_CONV):
+        R = C.CDLL(_REF_CONV)
+        fp = C.POINTER(C.c_float)
+        for name in ("ref_cpu_conv2d", "ref_cpu_conv2d_grad_weight", "ref_cpu_conv2d_grad_input"):
+            getattr(R, name).argtypes = [fp, fp, fp, C.POINTER(C.c_int), C.c_int]
+            getattr(R, name).restype = None
+        _ref_conv = R
+    return _ref_conv
+
+
+def ref_conv2d(x, w, shape, S=3):
+    oh, ow = conv_dims(shape)
+    return _conv_call(ref_conv().ref_cpu_conv2d, x, w, (shape[0], shape[4], oh, ow), shape, S, threads=False)
+
+
+def ref_conv2d_grad_weight(dy, x, shape, S=3):
+    return _conv_call(ref_conv().ref_cpu_conv2d_grad_weight, dy, x, (shape[4], shape[1], shape[5], shape[6]), shape, S, threads=False)
+
+
+def ref_conv2d_grad_input(dy, w, shape, S=3):
+    return _conv_call(ref_conv().ref_cpu_conv2d_grad_input, dy, w, shape[:4], shape, S, threads=False)
 
 
 def absmax(src, R, K, k_strided):

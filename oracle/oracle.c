@@ -20,6 +20,8 @@
  *   orc_gemm             repro_gemm_cuda/repro_gemm_cpu.h:25-51
  *   orc_gemm_partial     same dot products, cut to a k-range and left unrounded (what a K-shard holds)
  *   orc_round_partials   repro_gemm_cuda/repro_gemm.cu:156-165
+ *   orc_conv2d*          repro_conv_cuda/repro_conv_math.cuh:10-17, repro_conv_cpu.h:25-90 (pinned against
+ *                        the reference's cpu_conv2d* through tests/golden/conv_hashes.json and oracle/_ref)
  *   orc_fnv1a64          repro_gemm_cuda/repro_test_util.h:20-24
  *   orc_rng_* / fills    repro_gemm_cuda/repro_test_util.h:30-48, gpt2_ops_suite/gpt2_ops_suite.cu:59-76
  *
@@ -235,6 +237,123 @@ void orc_round_partials(const int64_t* T, int parts, const float* maxA, const fl
             int E = orc_scale_exponent(maxA[r]) + orc_scale_exponent(maxB[c]) - 14 * (S - 1);
             C[(size_t)r * N + c] = orc_round_to_float(t, E);
         }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Convolution (repro_conv_cuda/repro_conv_math.cuh:10-17, repro_conv_cpu.h:25-90).
+ * shape = {N, C, H, W, F, KH, KW, SY, SX, PY, PX}.  Forward and weight gradient are restated the
+ * way the reference's own test states them (test_repro_conv.cu:84-112): the GEMM definition on the
+ * im2col matrix.  The input gradient is restated directly: dY scaled per image, all weights with
+ * one scale, exact integer sum over the taps that touch a pixel, one rounding.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct { int N, C, H, W, F, KH, KW, SY, SX, PY, PX, OH, OW, K; } conv_t;
+
+static conv_t conv_shape(const int* s) {
+    conv_t g = {s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], 0, 0, 0};
+    g.OH = (g.H + 2 * g.PY - g.KH) / g.SY + 1;
+    g.OW = (g.W + 2 * g.PX - g.KW) / g.SX + 1;
+    g.K = g.C * g.KH * g.KW;
+    return g;
+}
+
+/* X[w][k]: value at position k = (c, ky, kx) of window w = (n, oy, ox); zero in the padding. */
+static float* conv_im2col(const float* x, const conv_t* g) {
+    size_t windows = (size_t)g->N * g->OH * g->OW;
+    float* X = (float*)malloc(sizeof(float) * windows * g->K);
+    if (!X) return NULL;
+    size_t at = 0;
+    for (int n = 0; n < g->N; ++n)
+        for (int oy = 0; oy < g->OH; ++oy)
+            for (int ox = 0; ox < g->OW; ++ox)
+                for (int c = 0; c < g->C; ++c)
+                    for (int ky = 0; ky < g->KH; ++ky)
+                        for (int kx = 0; kx < g->KW; ++kx) {
+                            int y = oy * g->SY - g->PY + ky, xx = ox * g->SX - g->PX + kx;
+                            X[at++] = (y < 0 || y >= g->H || xx < 0 || xx >= g->W)
+                                          ? 0.0f : x[(((size_t)n * g->C + c) * g->H + y) * g->W + xx];
+                        }
+    return X;
+}
+
+int orc_conv2d(const float* x, const float* w, float* out, const int* shape, int S, int threads) {
+    conv_t g = conv_shape(shape);
+    int per = g.OH * g.OW, windows = g.N * per;
+    float* X = conv_im2col(x, &g);
+    float* Y = (float*)malloc(sizeof(float) * (size_t)windows * g.F);
+    int rc = (X && Y) ? orc_gemm(X, w, Y, windows, g.F, g.K, 0, 1, S, threads) : -1;   /* Y = X W^T */
+    if (rc == 0)
+        for (int i = 0; i < windows; ++i)
+            for (int f = 0; f < g.F; ++f)
+                out[((size_t)(i / per) * g.F + f) * per + i % per] = Y[(size_t)i * g.F + f];
+    free(X); free(Y);
+    return rc;
+}
+
+int orc_conv2d_grad_weight(const float* dy, const float* x, float* dw, const int* shape, int S, int threads) {
+    conv_t g = conv_shape(shape);
+    int per = g.OH * g.OW, windows = g.N * per;
+    float* X = conv_im2col(x, &g);
+    float* D = (float*)malloc(sizeof(float) * (size_t)windows * g.F);
+    int rc = -1;
+    if (X && D) {
+        for (int i = 0; i < windows; ++i)
+            for (int f = 0; f < g.F; ++f)
+                D[(size_t)i * g.F + f] = dy[((size_t)(i / per) * g.F + f) * per + i % per];
+        rc = orc_gemm(D, X, dw, g.F, g.K, windows, 1, 0, S, threads);                  /* dW = D^T X */
+    }
+    free(X); free(D);
+    return rc;
+}
+
+typedef struct { conv_t g; const int32_t *D, *Wq; const int* eI; int eW, S; float* dx; } conv_dx_t;
+
+static void conv_dx_plane(int i, void* ctx) {     /* one (n, c) plane of dX */
+    conv_dx_t* t = (conv_dx_t*)ctx;
+    const conv_t* g = &t->g;
+    int n = i / g->C, c = i % g->C;
+    for (int y = 0; y < g->H; ++y)
+        for (int xx = 0; xx < g->W; ++xx) {
+            int64_t sum = 0;
+            for (int ky = 0; ky < g->KH; ++ky) {
+                int ry = y + g->PY - ky;
+                if (ry < 0 || ry % g->SY != 0 || ry / g->SY >= g->OH) continue;
+                for (int kx = 0; kx < g->KW; ++kx) {
+                    int rx = xx + g->PX - kx;
+                    if (rx < 0 || rx % g->SX != 0 || rx / g->SX >= g->OW) continue;
+                    for (int f = 0; f < g->F; ++f)
+                        sum += (int64_t)t->D[(((size_t)n * g->F + f) * g->OH + ry / g->SY) * g->OW + rx / g->SX] *
+                               t->Wq[(((size_t)f * g->C + c) * g->KH + ky) * g->KW + kx];
+                }
+            }
+            t->dx[(((size_t)n * g->C + c) * g->H + y) * g->W + xx] =
+                orc_round_to_float(sum, t->eI[n] + t->eW - 14 * (t->S - 1));
+        }
+}
+
+int orc_conv2d_grad_input(const float* dy, const float* w, float* dx, const int* shape, int S, int threads) {
+    conv_dx_t t;
+    t.g = conv_shape(shape);
+    size_t per = (size_t)t.g.F * t.g.OH * t.g.OW, nw = (size_t)t.g.F * t.g.K;
+    int32_t* D = (int32_t*)malloc(sizeof(int32_t) * per * t.g.N);
+    int32_t* Wq = (int32_t*)malloc(sizeof(int32_t) * nw);
+    int* eI = (int*)malloc(sizeof(int) * (size_t)t.g.N);
+    int ok = D && Wq && eI;
+    if (ok) {
+        for (int n = 0; n < t.g.N; ++n) {          /* dY: one scale per image */
+            float m = 0.0f;
+            for (size_t i = 0; i < per; ++i) m = fmaxf(m, fabsf(dy[n * per + i]));
+            eI[n] = orc_scale_exponent(m);
+            for (size_t i = 0; i < per; ++i) D[n * per + i] = orc_fixed_point(dy[n * per + i], eI[n], S);
+        }
+        float mw = 0.0f;                           /* weights: one scale for all */
+        for (size_t i = 0; i < nw; ++i) mw = fmaxf(mw, fabsf(w[i]));
+        t.eW = orc_scale_exponent(mw);
+        for (size_t i = 0; i < nw; ++i) Wq[i] = orc_fixed_point(w[i], t.eW, S);
+        t.D = D; t.Wq = Wq; t.eI = eI; t.S = S; t.dx = dx;
+        parallel_for(t.g.N * t.g.C, threads, conv_dx_plane, &t);
+    }
+    free(D); free(Wq); free(eI);
+    return ok ? 0 : -1;
 }
 
 /* ------------------------------------------------------------------------------------------

@@ -24,3 +24,10 @@ def golden():
 def scalar_vectors():
     with open(os.path.join(ROOT, "tests", "golden", "scalar_vectors.json")) as f:
         return json.load(f)
+
+
+@pytest.fixture(scope="session")
+def conv_golden():
+    with open(os.path.join(ROOT, "tests", "golden", "conv_hashes.json")) as f:
+        recs = json.load(f)
+    return {(r["name"], r["S"]): r for r in recs}

@@ -6,6 +6,7 @@ oracle/Makefile):
     python tests/golden/make_golden.py scalar        # tests/golden/scalar_vectors.json
     python tests/golden/make_golden.py gemm          # tests/golden/gemm_hashes.json (seconds to minutes)
     python tests/golden/make_golden.py c4            # adds the 16384^3 case (about ten minutes, 6 GiB)
+    python tests/golden/make_golden.py conv          # tests/golden/conv_hashes.json
 
 Every GEMM entry records the FNV-1a-64 of the inputs (A then B, chained) and of the output that
 repro_gemm_cuda/repro_gemm_cpu.h:25 (cpu_gemm) produced for them, so a test can regenerate the
@@ -159,6 +160,23 @@ def c4(path):
         json.dump(recs, f, indent=0)
 
 
+def conv_hashes():
+    """Forward, weight-gradient and input-gradient hashes from repro_conv_cuda/repro_conv_cpu.h:25,45,72."""
+    recs = []
+    for name, shape, dist in fx.CONV_CASES:
+        x, w, dy = fx.conv_inputs(shape, dist)
+        for S in (1, 2, 3):
+            rec = dict(name=name, shape=list(shape), dist=dist, S=S,
+                       in_hash="%016x" % oracle.fnv1a64(dy, oracle.fnv1a64(w, oracle.fnv1a64(x))),
+                       forward=oracle.hexhash(oracle.ref_conv2d(x, w, shape, S)),
+                       grad_weight=oracle.hexhash(oracle.ref_conv2d_grad_weight(dy, x, shape, S)),
+                       grad_input=oracle.hexhash(oracle.ref_conv2d_grad_input(dy, w, shape, S)))
+            print(rec, flush=True)
+            recs.append(rec)
+    with open(os.path.join(HERE, "conv_hashes.json"), "w") as f:
+        json.dump(recs, f, indent=0)
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     oracle.build()
@@ -171,3 +189,7 @@ if __name__ == "__main__":
         gemm_hashes(path)
     if what == "c4":
         c4(path)
+    if what in ("conv", "all"):
+        if oracle.ref_conv() is None:
+            sys.exit("the reference library oracle/_ref/librepro_ref_conv.so could not be built here")
+        conv_hashes()

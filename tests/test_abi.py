@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(L):
     header = open(os.path.join(ROOT, "include", "rgb200.h")).read()
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
     names = set(re.findall(r"\b(rgb200_[a-z0-9_]+)\s*\(", header))
-    assert len(names) >= 17
+    assert len(names) >= 23
     for n in sorted(names):
         assert hasattr(L, n), "librgb200.so does not export %s" % n
 
@@ -34,6 +34,37 @@ def test_cxx_shim_declares_the_reference_surface():
     for needle in ("namespace repro_gemm", "enum class Algo", "struct Config", "struct Plan", "make_plan",
                    "repro_gemm_fp32_ws", "repro_gemm_fp32", "algo_name", "MAX_SLICES"):
         assert needle in shim, needle
+
+
+def test_conv_shim_declares_the_reference_surface():
+    shim = open(os.path.join(ROOT, "include", "repro_conv.cuh")).read()
+    for needle in ("namespace repro_conv", "struct ConvShape", "conv2d_workspace", "conv2d_grad_weight_workspace",
+                   "conv2d_grad_input_workspace", "repro_conv2d_ws", "repro_conv2d_grad_weight_ws",
+                   "repro_conv2d_grad_input_ws", "int SY = 1, SX = 1", "int PY = 0, PX = 0"):
+        assert needle in shim, needle
+
+
+def test_conv_workspace_planning_and_shape_checks(L):
+    """Host-only: sizes depend on (shape, slices) alone; unsupported shapes give cudaErrorInvalidValue
+    (the reference's checks, repro_conv_cuda/repro_conv.cu:157-167)."""
+    from bit_reproducible_training_b200 import repro_conv as rc
+    g = rc.ConvShape(100, 1, 28, 28, 6, 5, 5, PY=2, PX=2)
+    assert (g.K(), g.OH(), g.OW(), g.windows(), g.output_size()) == (25, 28, 28, 78400, 100 * 6 * 784)
+    for query in (rc.conv2d_workspace, rc.conv2d_grad_weight_workspace, rc.conv2d_grad_input_workspace):
+        code, n3 = query(g, 3)
+        assert code == 0 and n3 > 0 and query(g, 3) == (0, n3)
+        assert query(g, 1)[1] < n3                      # fewer digit planes
+        assert query(g, 0)[0] == rg.cudaErrorInvalidValue and query(g, 4)[0] == rg.cudaErrorInvalidValue
+        for bad in (dict(N=0), dict(C=0), dict(F=0), dict(KH=0), dict(SY=0), dict(PX=-1), dict(KH=40), dict(N=70000),
+                    dict(N=60000, H=200, W=200)):     # the last: 2^31 or more input values
+            fields = dict(N=100, C=1, H=28, W=28, F=6, KH=5, KW=5, SY=1, SX=1, PY=2, PX=2)
+            fields.update(bad)
+            assert query(rc.ConvShape(**fields), 3)[0] == rg.cudaErrorInvalidValue, bad
+    # larger windows and filter counts than the reference's kernels take are planned here
+    assert rc.conv2d_workspace(rc.ConvShape(2, 160, 9, 9, 300, 3, 3, PY=1, PX=1), 3)[0] == 0
+    # more windows than an exact INT64 sum allows at S = 3 (9e18 / (127 * 128^2)^2 = 2 078 698)
+    assert rc.conv2d_grad_weight_workspace(rc.ConvShape(600, 1, 60, 60, 4, 1, 1), 3)[0] == rg.cudaErrorInvalidValue
+    assert rc.conv2d_grad_weight_workspace(rc.ConvShape(600, 1, 60, 60, 4, 1, 1), 2)[0] == 0
 
 
 def test_default_config_matches_reference_defaults(L):
