@@ -238,7 +238,12 @@ void launch_kmajor(const KmajorOperand& first, const KmajorOperand& second, int 
         split_kmajor_kernel<S, TPR, CH, VEC><<<dim3(b1 + b2, batch), PREPASS_THREADS, 0, st>>>(               \
             first, second, b1, K, Kp, zero_word);                                                             \
     } while (0)
-    if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS) RGB_KMAJOR(256, 1, false);
+    if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS) {      // general path: any K, any alignment; row group sized to the row
+        if (nq <= 64) RGB_KMAJOR(32, 1, false);
+        else if (nq <= 256) RGB_KMAJOR(64, 1, false);
+        else if (nq <= 1024) RGB_KMAJOR(128, 1, false);
+        else RGB_KMAJOR(256, 1, false);
+    }
     else if (nq <= 32 * 2) RGB_KMAJOR(32, 2, true);
     else if (nq <= 32 * 4) RGB_KMAJOR(32, 4, true);
     else if (nq <= 64 * 4) RGB_KMAJOR(64, 4, true);
@@ -463,6 +468,7 @@ bool conv_geometry(const rgb200_conv_shape* s, int S, ConvGeom& g) {
     g.N = s->N; g.C = s->C; g.H = s->H; g.W = s->W; g.F = s->F; g.KH = s->KH; g.KW = s->KW;
     g.SY = s->SY; g.SX = s->SX; g.PY = s->PY; g.PX = s->PX;
     g.OH = (int)OH; g.OW = (int)OW; g.K = s->C * s->KH * s->KW;
+    g.prepare();
     return true;
 }
 
@@ -489,32 +495,20 @@ cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint
     const int S = L.S;
     switch (c.kind) {
         case CONV_FORWARD: {          // A: the weights as stored, one copy of the planes per image; B: windows of image b
-            const StoredRows w{c.q, g.K};
-            launch_gather_max(w, max_a, L.M, L.K, 1, 0, 1, st);
-            launch_gather_split(S, w, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 1, st);   // every image reads the same filter maxima
-            const WindowsOfImage x{c.p, g};
-            launch_gather_max(x, max_b, L.N, L.K, L.batch, L.N, 1, st);
-            launch_gather_split(S, x, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, L.N, 1, st);
+            launch_gather_operand(S, StoredRows{c.q, g.K}, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, st);
+            launch_gather_operand(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, st);
             break;
         }
         case CONV_GRAD_WEIGHT: {      // A: dY by filter over all windows; B: window values by position over all windows
-            const FiltersOverWindows d{c.p, g};
-            launch_gather_max(d, max_a, L.M, L.K, 1, 0, 1, st);
-            launch_gather_split(S, d, max_a, qa, ea, L.M, L.K, L.Kp, 1, 0, 1, st);
-            const PositionsOverWindows x{c.q, g};
-            launch_gather_max(x, max_b, L.N, L.K, 1, 0, 1, st);
-            launch_gather_split(S, x, max_b, qb, eb, L.N, L.K, L.Kp, 1, 0, 1, st);
+            launch_gather_operand(S, FiltersOverWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, st);
+            launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, st);
             break;
         }
         case CONV_GRAD_INPUT: {       // A: weights by input channel, one scale for all; B: dY taps per pixel, one scale per image
-            const StoredRows all_w{c.q, (long long)g.F * g.K};
-            launch_gather_max(all_w, max_a, 1, g.F * g.K, 1, 0, 0, st);
-            const ChannelsOverTaps w{c.q, g};
-            launch_gather_split(S, w, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 0, st);
-            const StoredRows images{c.p, (long long)g.F * g.OH * g.OW};
-            launch_gather_max(images, max_b, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
-            const PixelsOverTaps d{c.p, g};
-            launch_gather_split(S, d, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, 1, 0, st);
+            launch_gather_max(StoredRows{c.q, (long long)g.F * g.K}, max_a, 1, g.F * g.K, 1, 0, 0, st);
+            launch_gather_operand(S, ChannelsOverTaps{c.q, g}, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, false, 0, 0, st);
+            launch_gather_max(StoredRows{c.p, (long long)g.F * g.OH * g.OW}, max_b, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
+            launch_gather_operand(S, PixelsOverTaps{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, false, 1, 0, st);
             break;
         }
     }

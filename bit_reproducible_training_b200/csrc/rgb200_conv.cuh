@@ -20,18 +20,46 @@
 
 namespace rgb200 {
 
+// Division of a non-negative 32-bit integer (below 2^31) by a fixed divisor as one multiply-high and a
+// shift: with p = 31 + ceil(log2 d) and mul = ceil(2^p / d), floor(n / d) = (n * mul) >> p for all such n.
+// The index maps divide by kernel and image extents for every element they fetch.
+struct FastDiv {
+    unsigned d, mul, shr;
+    FastDiv() : d(1), mul(0), shr(0) {}
+    explicit FastDiv(int divisor) : d((unsigned)divisor), mul(0), shr(0) {
+        if (d > 1) {
+            unsigned lg = 0;
+            while ((1ull << lg) < d) ++lg;
+            const unsigned p = 31 + lg;
+            mul = (unsigned)(((1ull << p) + d - 1) / d);
+            shr = p - 32;
+        }
+    }
+    __host__ __device__ __forceinline__ int div(int n) const {
+#ifdef __CUDA_ARCH__
+        return d == 1 ? n : (int)(__umulhi((unsigned)n, mul) >> shr);
+#else
+        return d == 1 ? n : (int)((((unsigned long long)(unsigned)n * mul) >> 32) >> shr);
+#endif
+    }
+};
+
 struct ConvGeom {
     int N, C, H, W, F, KH, KW, SY, SX, PY, PX;
     int OH, OW, K;            // output height and width, values per window
+    FastDiv by_khw, by_kw, by_ow, by_per, by_w, by_sy, by_sx;   // KH*KW, KW, OW, OH*OW, W, SY, SX
+    void prepare() {
+        by_khw = FastDiv(KH * KW); by_kw = FastDiv(KW); by_ow = FastDiv(OW); by_per = FastDiv(OH * OW);
+        by_w = FastDiv(W); by_sy = FastDiv(SY); by_sx = FastDiv(SX);
+    }
 };
 
 // ---------------------------------------------------------------------------------------------
 // Index maps: at(b, r, k) is element (row r, index k) of operand matrix number b.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float conv_window_value(const float* __restrict__ x, const ConvGeom& g, int n, int oy, int ox, int k) {
-    const int khw = g.KH * g.KW;
-    const int c = k / khw, rem = k - c * khw;
-    const int ky = rem / g.KW, kx = rem - ky * g.KW;
+    const int c = g.by_khw.div(k), rem = k - c * (g.KH * g.KW);
+    const int ky = g.by_kw.div(rem), kx = rem - ky * g.KW;
     const int y = oy * g.SY - g.PY + ky, xx = ox * g.SX - g.PX + kx;
     if ((unsigned)y >= (unsigned)g.H || (unsigned)xx >= (unsigned)g.W) return 0.0f;   // zero padding
     return __ldg(x + (((size_t)n * g.C + c) * g.H + y) * g.W + xx);
@@ -40,7 +68,7 @@ __device__ __forceinline__ float conv_window_value(const float* __restrict__ x, 
 struct WindowsOfImage {      // forward: b = image, r = window (oy, ox) of that image, k = position
     const float* x; ConvGeom g;
     __device__ __forceinline__ float at(int b, int r, int k) const {
-        const int oy = r / g.OW;
+        const int oy = g.by_ow.div(r);
         return conv_window_value(x, g, b, oy, r - oy * g.OW, k);
     }
 };
@@ -48,9 +76,8 @@ struct WindowsOfImage {      // forward: b = image, r = window (oy, ox) of that 
 struct PositionsOverWindows {   // weight gradient: r = position, k = window (n, oy, ox)
     const float* x; ConvGeom g;
     __device__ __forceinline__ float at(int, int r, int k) const {
-        const int per = g.OH * g.OW;
-        const int n = k / per, j = k - n * per;
-        const int oy = j / g.OW;
+        const int n = g.by_per.div(k), j = k - n * (g.OH * g.OW);
+        const int oy = g.by_ow.div(j);
         return conv_window_value(x, g, n, oy, j - oy * g.OW, r);
     }
 };
@@ -59,7 +86,7 @@ struct FiltersOverWindows {     // weight gradient: r = filter, k = window (n, o
     const float* dy; ConvGeom g;
     __device__ __forceinline__ float at(int, int r, int k) const {
         const int per = g.OH * g.OW;
-        const int n = k / per, j = k - n * per;
+        const int n = g.by_per.div(k), j = k - n * per;
         return __ldg(dy + ((size_t)n * g.F + r) * per + j);
     }
 };
@@ -68,7 +95,7 @@ struct ChannelsOverTaps {       // input gradient: r = input channel, k = (f, ky
     const float* w; ConvGeom g;
     __device__ __forceinline__ float at(int, int r, int k) const {
         const int khw = g.KH * g.KW;
-        const int f = k / khw, rem = k - f * khw;
+        const int f = g.by_khw.div(k), rem = k - f * khw;
         return __ldg(w + ((size_t)f * g.C + r) * khw + rem);
     }
 };
@@ -76,14 +103,13 @@ struct ChannelsOverTaps {       // input gradient: r = input channel, k = (f, ky
 struct PixelsOverTaps {         // input gradient: b = image, r = pixel (y, x), k = (f, ky, kx)
     const float* dy; ConvGeom g;
     __device__ __forceinline__ float at(int b, int r, int k) const {
-        const int khw = g.KH * g.KW;
-        const int f = k / khw, rem = k - f * khw;
-        const int ky = rem / g.KW, kx = rem - ky * g.KW;
-        const int y = r / g.W, xx = r - y * g.W;
+        const int f = g.by_khw.div(k), rem = k - f * (g.KH * g.KW);
+        const int ky = g.by_kw.div(rem), kx = rem - ky * g.KW;
+        const int y = g.by_w.div(r), xx = r - y * g.W;
         // the window whose tap (ky, kx) lies on this pixel, if the strides allow one
         const int ry = y + g.PY - ky, rx = xx + g.PX - kx;
         if (ry < 0 || rx < 0) return 0.0f;
-        const int oy = ry / g.SY, ox = rx / g.SX;
+        const int oy = g.by_sy.div(ry), ox = g.by_sx.div(rx);
         if (oy * g.SY != ry || ox * g.SX != rx || oy >= g.OH || ox >= g.OW) return 0.0f;
         return __ldg(dy + (((size_t)b * g.F + f) * g.OH + oy) * g.OW + ox);
     }
@@ -145,6 +171,69 @@ gather_split_kernel(const Source src, const uint32_t* __restrict__ maxbits, int8
     }
 }
 
+// Short rows (Kp <= 128 * QUADS): one warp keeps a whole row in registers between the maximum and the
+// split, so the index map is evaluated once per element and one launch does both steps.  With
+// OWN_MAX = false the scale comes from a maximum reduced beforehand (shared by several rows).
+// grid = (ceil(R / 8), 1, batch), 256 threads
+template <int S, class Source, int QUADS, bool OWN_MAX>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+gather_rows_kernel(const Source src, const uint32_t* __restrict__ maxbits, int8_t* __restrict__ planes,
+                   int* __restrict__ expo, int R, int K, int Kp, int slot_batch_mul, int slot_row_mul) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5);
+    const int b = blockIdx.z;
+    if (row >= R) return;
+    float4 v[QUADS];
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < QUADS; ++i) {
+        const int k = (lane + 32 * i) * 4;
+        v[i].x = k + 0 < K ? src.at(b, row, k + 0) : 0.0f;
+        v[i].y = k + 1 < K ? src.at(b, row, k + 1) : 0.0f;
+        v[i].z = k + 2 < K ? src.at(b, row, k + 2) : 0.0f;
+        v[i].w = k + 3 < K ? src.at(b, row, k + 3) : 0.0f;
+        if (OWN_MAX) m = abs4max(m, v[i]);
+    }
+    if (OWN_MAX) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    } else {
+        m = bits_f32(maxbits[(size_t)b * slot_batch_mul + (size_t)row * slot_row_mul]);
+    }
+    const int e = scale_exponent(m);
+    if (lane == 0) expo[(size_t)b * R + row] = e;
+    const QuantScale q = quant_scale(e, S);
+    const bool plain = plain_row(e);
+    const size_t plane_stride = (size_t)R * Kp;
+    int8_t* out = planes + (size_t)b * S * plane_stride + (size_t)row * Kp;
+#pragma unroll
+    for (int i = 0; i < QUADS; ++i) {
+        const int k = (lane + 32 * i) * 4;
+        if (k < Kp) store_quad<S>(v[i], q, plain, out, plane_stride, (size_t)k);
+    }
+}
+
+template <int S, class Source, bool OWN_MAX>
+void launch_gather_rows_s(const Source& src, const uint32_t* maxbits, int8_t* planes, int* expo, int R, int K, int Kp,
+                          int batch, int slot_batch_mul, int slot_row_mul, cudaStream_t st) {
+    const dim3 grid((R + 7) / 8, 1, batch);
+#define RGB_ROWS(Q) gather_rows_kernel<S, Source, Q, OWN_MAX><<<grid, PREPASS_THREADS, 0, st>>>( \
+        src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul)
+    if (Kp <= 128) RGB_ROWS(1);
+    else if (Kp <= 256) RGB_ROWS(2);
+    else if (Kp <= 512) RGB_ROWS(4);
+    else RGB_ROWS(8);
+#undef RGB_ROWS
+}
+
+constexpr int GATHER_ROWS_MAX_KP = 1024;       // longest padded row the one-launch form keeps in registers
+
+// One operand through the gather pre-pass.  own_max: every row has its own scale (its slot is
+// b * R + r); otherwise the maxima were reduced beforehand into the given slots.
+template <class Source>
+void launch_gather_operand(int S, const Source& src, uint32_t* maxbits, int8_t* planes, int* expo, int R, int K, int Kp,
+                           int batch, bool own_max, int slot_batch_mul, int slot_row_mul, cudaStream_t st);
+
 template <class Source>
 void launch_gather_max(const Source& src, uint32_t* maxbits, int R, int K, int batch, int slot_batch_mul, int slot_row_mul,
                        cudaStream_t st) {
@@ -161,6 +250,26 @@ void launch_gather_split(int S, const Source& src, const uint32_t* maxbits, int8
         case 2: gather_split_kernel<2, Source><<<grid, PREPASS_THREADS, 0, st>>>(src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul); break;
         default: gather_split_kernel<3, Source><<<grid, PREPASS_THREADS, 0, st>>>(src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul); break;
     }
+}
+
+template <class Source>
+void launch_gather_operand(int S, const Source& src, uint32_t* maxbits, int8_t* planes, int* expo, int R, int K, int Kp,
+                           int batch, bool own_max, int slot_batch_mul, int slot_row_mul, cudaStream_t st) {
+    if (Kp > GATHER_ROWS_MAX_KP) {             // long rows: maxima by atomics over chunks, then the split
+        if (own_max) {
+            slot_batch_mul = R; slot_row_mul = 1;
+            launch_gather_max(src, maxbits, R, K, batch, slot_batch_mul, slot_row_mul, st);
+        }
+        launch_gather_split(S, src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, st);
+        return;
+    }
+#define RGB_OPERAND(SS)                                                                                                  \
+    do {                                                                                                                 \
+        if (own_max) launch_gather_rows_s<SS, Source, true>(src, maxbits, planes, expo, R, K, Kp, batch, 0, 0, st);       \
+        else launch_gather_rows_s<SS, Source, false>(src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, st); \
+    } while (0)
+    if (S == 1) RGB_OPERAND(1); else if (S == 2) RGB_OPERAND(2); else RGB_OPERAND(3);
+#undef RGB_OPERAND
 }
 
 }  // namespace rgb200
