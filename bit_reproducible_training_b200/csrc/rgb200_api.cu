@@ -75,7 +75,8 @@ int auto_split(int M, int N, int batch, int k_blocks, int tile_n) {
 
 // sum_limit bounds total_k * max|X|^2, the largest magnitude an exact sum can reach.
 cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const rgb200_config& cfg,
-                        bool partial_out, Layout& L, double sum_limit = 4611686018427387904.0 /* 2^62 */) {
+                        bool partial_out, Layout& L, double sum_limit = 4611686018427387904.0 /* 2^62 */,
+                        bool auto_ranges = true) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || cfg.split_k <= 0 || total_k < K) return cudaErrorInvalidValue;
     if (cfg.slices < 1 || cfg.slices > 3) return cudaErrorInvalidValue;
     if (cfg.algo < RGB200_ALGO_AUTO || cfg.algo > RGB200_ALGO_TENSORCORE) return cudaErrorInvalidValue;
@@ -96,7 +97,7 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
         L.split = 1;            // the INT64 verification kernel never needs K ranges
     } else {
         int want = cfg.split_k;
-        if (want == 1 && !partial_out) want = auto_split(M, N, batch, L.k_blocks, tile_n_for(S, N));
+        if (want == 1 && !partial_out && auto_ranges) want = auto_split(M, N, batch, L.k_blocks, tile_n_for(S, N));
         L.split = want > L.min_split ? want : L.min_split;
         if (L.split > L.k_blocks) L.split = L.k_blocks;
     }
@@ -137,9 +138,9 @@ struct DeviceInfo {
 DeviceInfo g_dev[MAX_DEVICES];
 std::once_flag g_dev_once[MAX_DEVICES];
 
-template <int S, int NT>
+template <int S, int NT, bool IMAGE_MAJOR_C = false>
 cudaError_t set_kernel_attrs() {
-    return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<S, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<S, NT, IMAGE_MAJOR_C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 GemmTraits<S, NT>::SMEM_BYTES);
 }
 
@@ -162,7 +163,11 @@ cudaError_t device_info(const DeviceInfo** out) {
         if (d.cc == 100) {   // the only architecture this library carries code for
             if ((e2 = set_kernel_attrs<1, 64>()) != cudaSuccess || (e2 = set_kernel_attrs<2, 64>()) != cudaSuccess ||
                 (e2 = set_kernel_attrs<3, 64>()) != cudaSuccess || (e2 = set_kernel_attrs<1, 256>()) != cudaSuccess ||
-                (e2 = set_kernel_attrs<2, 96>()) != cudaSuccess) { d.err = e2; return; }
+                (e2 = set_kernel_attrs<2, 96>()) != cudaSuccess || (e2 = set_kernel_attrs<1, 64, true>()) != cudaSuccess ||
+                (e2 = set_kernel_attrs<2, 64, true>()) != cudaSuccess || (e2 = set_kernel_attrs<3, 64, true>()) != cudaSuccess) {
+                d.err = e2;
+                return;
+            }
             d.attrs_set = true;
             if (cudaStreamCreateWithFlags(&d.side, cudaStreamNonBlocking) != cudaSuccess ||
                 cudaEventCreateWithFlags(&d.fork_ev, cudaEventDisableTiming) != cudaSuccess ||
@@ -313,6 +318,7 @@ struct RunArgs {
     long long* const* scatter = nullptr;   // per-owner destination buffers of the INT64 sums (K-sharded), or null
     int scatter_world = 0, scatter_rank = 0;
     const PrepassHook* hook = nullptr;
+    int c_image_rows = 0;                  // > 0: image-major C (see GemmParams::c_image_rows); needs split == 1
 };
 
 template <int S>
@@ -378,7 +384,8 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         return cudaGetLastError();
     }
 
-    const int tile_n = tile_n_for(S, L.N);
+    if (a.c_image_rows && (L.split != 1 || L.batch != 1 || part)) return cudaErrorInvalidValue;
+    const int tile_n = a.c_image_rows ? TILE_N_BASE : tile_n_for(S, L.N);
     CUtensorMap map_a, map_b;
     if ((e = encode_planes_map(&map_a, qa, L.M, L.Kp, S, L.batch, BLOCK_M)) != cudaSuccess) return e;
     if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, tile_n)) != cudaSuccess) return e;
@@ -395,6 +402,7 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     P.n_tiles = ceil_div(L.N, tile_n);
     P.e0 = e0;
     P.scatter_rows = 0; P.scatter_slot = 0;
+    P.c_image_rows = a.c_image_rows;
     for (int i = 0; i < 8; ++i) P.scatter[i] = nullptr;
     if (a.scatter) {
         P.scatter_rows = L.M / a.scatter_world;
@@ -405,7 +413,9 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     }
     const long long tiles = (long long)L.batch * L.split * P.m_tiles * P.n_tiles;
     const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
-    if (S == 1 && tile_n == 256)
+    if (a.c_image_rows)
+        gemm_i8_tcgen05_kernel<S, TILE_N_BASE, true><<<grid, GEMM_THREADS, GemmTraits<S, TILE_N_BASE>::SMEM_BYTES, a.st>>>(map_a, map_b, P);
+    else if (S == 1 && tile_n == 256)
         gemm_i8_tcgen05_kernel<1, 256><<<grid, GEMM_THREADS, GemmTraits<1, 256>::SMEM_BYTES, a.st>>>(map_a, map_b, P);
     else if (S == 2 && tile_n == 96)
         gemm_i8_tcgen05_kernel<2, 96><<<grid, GEMM_THREADS, GemmTraits<2, 96>::SMEM_BYTES, a.st>>>(map_a, map_b, P);
@@ -472,43 +482,71 @@ bool conv_geometry(const rgb200_conv_shape* s, int S, ConvGeom& g) {
     return true;
 }
 
+// Orientation of forward and input gradient: the many-row operand (windows, pixels) on the row side with
+// the image-major store, unless K needs several INT32 accumulation passes (then one product per image).
+bool conv_rows_are_places(ConvKind kind, const ConvGeom& g, int S) {
+    if (kind == CONV_GRAD_WEIGHT) return false;
+    const long long k = kind == CONV_FORWARD ? (long long)g.K : (long long)g.F * g.KH * g.KW;
+    const long long rows = kind == CONV_FORWARD ? (long long)g.N * g.OH * g.OW : (long long)g.N * g.H * g.W;
+    return k <= max_k_per_pass(S) / BLOCK_K * BLOCK_K && rows <= 0x7FFFFFFFll;
+}
+
 cudaError_t conv_layout(ConvKind kind, const ConvGeom& g, int S, Layout& L) {
     rgb200_config cfg;
     rgb200_default_config(&cfg);
     cfg.slices = S;
     cfg.algo = RGB200_ALGO_TENSORCORE;
     const double no_limit = 1.0e300;             // conv_geometry has bounded the sums already
+    const bool places = conv_rows_are_places(kind, g, S);
     switch (kind) {
-        case CONV_FORWARD: return plan_layout(g.F, g.OH * g.OW, g.K, g.K, g.N, cfg, false, L, no_limit);
+        case CONV_FORWARD:
+            if (places) return plan_layout(g.N * g.OH * g.OW, g.F, g.K, g.K, 1, cfg, false, L, no_limit, false);
+            return plan_layout(g.F, g.OH * g.OW, g.K, g.K, g.N, cfg, false, L, no_limit);
         case CONV_GRAD_WEIGHT: { const int w = g.N * g.OH * g.OW; return plan_layout(g.F, g.K, w, w, 1, cfg, false, L, no_limit); }
-        case CONV_GRAD_INPUT: { const int t = g.F * g.KH * g.KW; return plan_layout(g.C, g.H * g.W, t, t, g.N, cfg, false, L, no_limit); }
+        case CONV_GRAD_INPUT: {
+            const int t = g.F * g.KH * g.KW;
+            if (places) return plan_layout(g.N * g.H * g.W, g.C, t, t, 1, cfg, false, L, no_limit, false);
+            return plan_layout(g.C, g.H * g.W, t, t, g.N, cfg, false, L, no_limit);
+        }
     }
     return cudaErrorInvalidValue;
 }
 
-struct ConvCall { ConvKind kind; ConvGeom g; const float* p; const float* q; };   // (x, weight), (dy, x) or (dy, weight)
+struct ConvCall { ConvKind kind; ConvGeom g; const float* p; const float* q; bool places; };   // (x, weight), (dy, x) or (dy, weight)
 
 cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint32_t* max_b, int8_t* qa, int8_t* qb,
                          int* ea, int* eb, cudaStream_t st) {
     const ConvCall& c = *static_cast<const ConvCall*>(ctx);
     const ConvGeom& g = c.g;
     const int S = L.S;
+    const FastDiv one;
     switch (c.kind) {
-        case CONV_FORWARD: {          // A: the weights as stored, one copy of the planes per image; B: windows of image b
-            launch_gather_operand(S, StoredRows{c.q, g.K}, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, st);
-            launch_gather_operand(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, st);
+        case CONV_FORWARD:
+            if (c.places) {           // A: every window of every image; B: the weights as stored
+                launch_gather_operand(S, AllWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
+                launch_gather_operand(S, StoredRows{c.q, g.K}, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+            } else {                  // per image: A the weights (one copy of the planes per image), B the windows of image b
+                launch_gather_operand(S, StoredRows{c.q, g.K}, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                launch_gather_operand(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+            }
             break;
-        }
-        case CONV_GRAD_WEIGHT: {      // A: dY by filter over all windows; B: window values by position over all windows
-            launch_gather_operand(S, FiltersOverWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, st);
-            launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, st);
+        case CONV_GRAD_WEIGHT:        // A: dY by filter over all windows; B: window values by position over all windows
+            launch_gather_operand(S, FiltersOverWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
+            launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
             break;
-        }
-        case CONV_GRAD_INPUT: {       // A: weights by input channel, one scale for all; B: dY taps per pixel, one scale per image
-            launch_gather_max(StoredRows{c.q, (long long)g.F * g.K}, max_a, 1, g.F * g.K, 1, 0, 0, st);
-            launch_gather_operand(S, ChannelsOverTaps{c.q, g}, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, false, 0, 0, st);
-            launch_gather_max(StoredRows{c.p, (long long)g.F * g.OH * g.OW}, max_b, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
-            launch_gather_operand(S, PixelsOverTaps{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, false, 1, 0, st);
+        case CONV_GRAD_INPUT: {       // dY taps per pixel with one scale per image; weights by input channel with one scale for all
+            uint32_t* max_w = c.places ? max_b : max_a;
+            uint32_t* max_img = c.places ? max_a : max_b;     // N words: both regions hold at least N (rows >= N, batch >= N)
+            launch_gather_max(StoredRows{c.q, (long long)g.F * g.K}, max_w, 1, g.F * g.K, 1, 0, 0, st);
+            launch_gather_max(StoredRows{c.p, (long long)g.F * g.OH * g.OW}, max_img, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
+            if (c.places) {
+                launch_gather_operand(S, AllPixelsOverTaps{c.p, g, FastDiv(g.H * g.W)}, max_img, qa, ea, L.M, L.K, L.Kp, 1, false, 0, 1,
+                                      FastDiv(g.H * g.W), st);
+                launch_gather_operand(S, ChannelsOverTaps{c.q, g}, max_w, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 0, one, st);
+            } else {
+                launch_gather_operand(S, ChannelsOverTaps{c.q, g}, max_w, qa, ea, L.M, L.K, L.Kp, L.batch, false, 0, 0, one, st);
+                launch_gather_operand(S, PixelsOverTaps{c.p, g}, max_img, qb, eb, L.N, L.K, L.Kp, L.batch, false, 1, 0, one, st);
+            }
             break;
         }
     }
@@ -534,11 +572,12 @@ cudaError_t conv_run(ConvKind kind, const float* p, const float* q, float* out, 
     if (!p || !q || !out || !ws || ws_bytes < L.total) return cudaErrorInvalidValue;
     const DeviceInfo* dev = nullptr;
     if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
-    const ConvCall call{kind, g, p, q};
+    const ConvCall call{kind, g, p, q, conv_rows_are_places(kind, g, S)};
     const PrepassHook hook{conv_prepass, &call};
     RunArgs a{nullptr, nullptr, out, nullptr, nullptr, nullptr, 0, 0, (long long)L.M * L.N, false, true,
               static_cast<char*>(ws), static_cast<cudaStream_t>(stream), nullptr};
     a.hook = &hook;
+    if (call.places) a.c_image_rows = kind == CONV_FORWARD ? g.OH * g.OW : g.H * g.W;
     return dispatch(L, a, *dev);
 }
 

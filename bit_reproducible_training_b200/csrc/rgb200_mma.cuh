@@ -96,6 +96,11 @@ struct GemmParams {
     // scatter_rows == 0: off; otherwise a multiple of 128.
     long long* scatter[8];
     int scatter_rows, scatter_slot;
+    // Image-major C (kernels built with IMAGE_MAJOR_C): row r = image * c_image_rows + place, and element
+    // (r, col) is stored at C[(image * N + col) * c_image_rows + place], the [N, F, OH, OW] / [N, C, H, W]
+    // layouts of a convolution's results.  A warp's 32 rows are consecutive places, so each column is one
+    // 128-byte store.  0 in the row-major kernels.
+    int c_image_rows;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -275,7 +280,9 @@ __device__ __forceinline__ void cursor_next(KCursor& c, const GemmParams& P, lon
     if (c.valid) { c.tc = tile_coord(P, c.tile); c.kb = c.tc.kb_begin; }
 }
 
-template <int S, int NT>
+// IMAGE_MAJOR_C (the convolutions): the rows of the product are (image, place) pairs and C is stored
+// [image][column][place], see GemmParams::c_image_rows; only the FP32 store of the epilogue differs.
+template <int S, int NT, bool IMAGE_MAJOR_C = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmParams P) {
@@ -489,6 +496,20 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         r[3] = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
                     }
                 };
+                if (IMAGE_MAJOR_C) {
+                    // lanes are consecutive places of an image: every column is one contiguous 128-byte store per warp
+                    const int image = row / P.c_image_rows, place = row - image * P.c_image_rows;
+                    dst = reinterpret_cast<uint32_t*>(P.C) + ((size_t)image * P.N + col0) * P.c_image_rows + place;
+#pragma unroll
+                    for (int j = 0; j < CPT; j += 4) {
+                        uint32_t r[4];
+                        round4(j, r);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col0 + j + q < P.N) dst[(size_t)(j + q) * P.c_image_rows] = r[q];
+                    }
+                    continue;
+                }
                 const int past = (int)((reinterpret_cast<uintptr_t>(dst) >> 2) & 3);    // elements past a 16-byte boundary
                 if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && col0 + CPT <= P.N) {
                     // sector-aligned row segment: round eight, store one full 32-byte sector

@@ -277,6 +277,10 @@ CONV_CASES = [
     ("wide.range", (3, 5, 11, 9, 12, 3, 3, 1, 2, 1, 0), "wide"),
     # enough windows that the weight gradient is cut into several accumulation ranges
     ("many.windows", (64, 3, 48, 48, 8, 3, 3, 1, 1, 1, 1), "normal"),
+    # more than 105 472 values per window / taps per pixel: the forward (first) and the input gradient
+    # (second) need several INT32 accumulation passes at S = 3 and take the one-product-per-image form
+    ("long.window", (2, 300, 19, 19, 2, 19, 19, 1, 1, 9, 9), "normal"),
+    ("long.taps", (2, 2, 19, 19, 300, 19, 19, 1, 1, 9, 9), "normal"),
 ]
 
 
