@@ -195,6 +195,92 @@ def auxiliary_workload(args):
                           for c in cases), "l2": "512 MiB buffer written between timed iterations (L2 flush)"}}), flush=True)
 
 
+CONV_BENCH_SHAPES = {
+    # the two layers the reference's own convolution benchmark times (repro_conv_cuda/bench_repro_conv.cu:64-66)
+    "conv-lenet1": (100, 1, 28, 28, 6, 5, 5, 1, 1, 2, 2),
+    "conv-lenet2": (100, 6, 14, 14, 16, 5, 5, 1, 1, 0, 0),
+    # a mid-size layer (64 -> 64 channels, 3 x 3, 56 x 56 images, batch 32) where the products are large enough for tensor cores
+    "conv-mid": (32, 64, 56, 56, 64, 3, 3, 1, 1, 1, 1),
+}
+
+
+def conv_workload(args):
+    """Times the convolution forward, weight gradient and input gradient of one layer on one GPU (device-resident
+    tensors, CUDA events, L2 flushed between steps), checks the three results against the reference's CPU code
+    (or the restated oracle where that library is absent) and times that CPU code beside it."""
+    import torch
+    import oracle
+    from bit_reproducible_training_b200 import fixtures as fx
+    from bit_reproducible_training_b200 import repro_conv as rc
+    from bit_reproducible_training_b200 import repro_gemm as rg
+    torch.cuda.set_device(0)
+    shape = CONV_BENCH_SHAPES[args.workload]
+    g = rc.ConvShape(*shape)
+    x, w, dy = fx.conv_inputs(shape)
+    dx_, dw_, ddy = (torch.from_numpy(t).cuda() for t in (x, w, dy))
+    calls = []
+    for name, query, fn, a, b, n_out in (
+            ("forward", rc.conv2d_workspace, rc.repro_conv2d_ws, dx_, dw_, g.output_size()),
+            ("grad_weight", rc.conv2d_grad_weight_workspace, rc.repro_conv2d_grad_weight_ws, ddy, dx_, g.weight_size()),
+            ("grad_input", rc.conv2d_grad_input_workspace, rc.repro_conv2d_grad_input_ws, ddy, dw_, g.input_size())):
+        code, nbytes = query(g, SLICES)
+        if code != 0:
+            raise rg.ReproGemmError(code, name + " workspace")
+        calls.append((name, fn, a, b, torch.empty(n_out, dtype=torch.float32, device="cuda"),
+                      torch.empty(nbytes, dtype=torch.uint8, device="cuda")))
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def run(call):
+        name, fn, a, b, out, ws = call
+        code = fn(a, b, out, g, SLICES, ws)
+        if code != 0:
+            raise rg.ReproGemmError(code, name)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        for call in calls:
+            run(call)
+    torch.cuda.synchronize()
+    ms = {}
+    for call in calls:
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in ev:
+            flush.zero_()
+            a.record()
+            run(call)
+            b.record()
+        torch.cuda.synchronize()
+        ms[call[0]] = statistics.median(a.elapsed_time(b) for a, b in ev)
+    total_ms = sum(ms.values())
+    flops = 3 * 2.0 * g.windows() * g.F * g.K()
+
+    use_ref = oracle.ref_conv() is not None
+    cpu_fns = (oracle.ref_conv2d, oracle.ref_conv2d_grad_weight, oracle.ref_conv2d_grad_input) if use_ref else \
+              (oracle.conv2d, oracle.conv2d_grad_weight, oracle.conv2d_grad_input)
+    t0 = time.perf_counter()
+    want = [cpu_fns[0](x, w, shape, SLICES), cpu_fns[1](dy, x, shape, SLICES), cpu_fns[2](dy, w, shape, SLICES)]
+    cpu_s = time.perf_counter() - t0
+    ok = all(rg.fnv1a64(call[4]) == oracle.fnv1a64(ref) for call, ref in zip(calls, want))
+    peaks = measured_peaks()
+    mma_ops = 2.0 * SLICES * SLICES * g.windows() * g.F * g.K()
+    achieved = mma_ops / (ms["forward"] * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "bit-exact conv2d forward + both gradients, effective TFLOP/s (3 x 2 x windows x F x K / t), S=3",
+        "value": flops / (total_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": total_ms, "higher_is_better": True, "dtype": "int8", "data": "synthetic", "auxiliary": True,
+        "output_matches_cpu_reference": ok, "stages": {k + "_ms": v for k, v in ms.items()},
+        "config": {"workload": "%s: x[%d,%d,%d,%d], weight[%d,%d,%d,%d], stride (%d,%d), padding (%d,%d); %d windows of %d values"
+                               % (args.workload, g.N, g.C, g.H, g.W, g.F, g.C, g.KH, g.KW, g.SY, g.SX, g.PY, g.PX, g.windows(), g.K()),
+                   "l2": "512 MiB buffer written between timed iterations (L2 flush)"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": 2.0 * peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / (2.0 * peaks["bf16_tflops"]), "traffic": None,
+                     "note": "whole forward call (gather pre-pass + MMA kernel), int8 ops of the slice-pair MMAs on the "
+                             "unpadded problem; peak = 2 x the %s dense bf16 cuBLAS rate" % peaks["source"]},
+        "cpu_baseline": {"value": flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": oracle.default_threads(),
+                         "kind": "reference" if use_ref else "port",
+                         "sample": "the whole layer once: forward, weight gradient, input gradient (%.2f s)" % cpu_s}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -204,9 +290,9 @@ def main():
     ap.add_argument("--mode", default="rows", choices=["rows", "ksplit", "ksplit-fused"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--check", action="store_true", help="also compare the output hash with the golden value")
-    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"],
-                    help="c3 (default) is the headline 4096^3 workload; the others time the remaining configurations "
-                         "on one GPU and print a reduced line (no e2e, no CPU baseline)")
+    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"] + sorted(CONV_BENCH_SHAPES),
+                    help="c3 (default) is the headline 4096^3 workload; c1, c2, c4, c5 time the remaining GEMM configurations "
+                         "and conv-* one convolution layer (forward and both gradients) on one GPU, with a reduced line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -217,7 +303,7 @@ def main():
         return
     if args.workload != "c3":
         if rank == 0:
-            auxiliary_workload(args)
+            conv_workload(args) if args.workload in CONV_BENCH_SHAPES else auxiliary_workload(args)
         return
 
     import numpy as np

@@ -62,12 +62,17 @@ constexpr int PLAN_SM_COUNT = 148;       // B200; the plan must not depend on a 
 int auto_split(int M, int N, int batch, int k_blocks, int tile_n) {
     const long long tiles = (long long)batch * ceil_div(M, BLOCK_M) * ceil_div(N, tile_n);
     if (tiles >= PLAN_SM_COUNT || k_blocks < 16) return 1;
-    if ((double)M * N * batch * sizeof(long long) > 32.0 * 1024 * 1024) return 1;   // keep the partial buffers small
+    const double out_bytes = (double)M * N * batch * sizeof(long long);
+    if (out_bytes > 32.0 * 1024 * 1024) return 1;   // keep the partial buffers small
+    // Cost in units of one k block of MMA work on one SM (about 0.35 us, the time HBM moves 2.3 MB): sequential
+    // k blocks per SM, a fixed charge for the extra reduction kernel, and per range a small tail charge plus
+    // the write and read of that range's INT64 sums.  A tiny output (the weight gradient of a small
+    // convolution: 6 x 25 outputs over 78 400 windows) therefore spreads its K over up to 64 SMs.
+    const double per_range = 0.25 + 2.0 * out_bytes / 2.3e6;
     int best = 1;
     double best_cost = (double)ceil_div((int)tiles, PLAN_SM_COUNT) * k_blocks;
-    for (int s = 2; s <= 16 && s * 8 <= k_blocks; ++s) {
-        // per-SM sequential work in k blocks, plus a charge for the extra reduction kernel and its INT64 traffic
-        double cost = (double)((tiles * s + PLAN_SM_COUNT - 1) / PLAN_SM_COUNT) * ceil_div(k_blocks, s) + 8.0 + s;
+    for (int s = 2; s <= 64 && s * 8 <= k_blocks; ++s) {
+        double cost = (double)((tiles * s + PLAN_SM_COUNT - 1) / PLAN_SM_COUNT) * ceil_div(k_blocks, s) + 8.0 + s * per_range;
         if (cost < best_cost * 0.9) { best_cost = cost; best = s; }
     }
     return best;

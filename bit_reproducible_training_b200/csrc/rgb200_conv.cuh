@@ -81,13 +81,33 @@ __device__ __forceinline__ float conv_window_value(const float* __restrict__ x, 
     return __ldg(x + (((size_t)n * g.C + c) * g.H + y) * g.W + xx);
 }
 
+// Positions k .. k+3 of one window: (c, ky, kx) is found once and stepped with carries.
+__device__ __forceinline__ float4 conv_window_quad(const float* __restrict__ x, const ConvGeom& g, int n, int oy, int ox, int k, int K) {
+    int c = g.by_khw.div(k);
+    const int rem = k - c * (g.KH * g.KW);
+    int ky = g.by_kw.div(rem), kx = rem - ky * g.KW;
+    const int y0 = oy * g.SY - g.PY, x0 = ox * g.SX - g.PX;
+    float e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int y = y0 + ky, xx = x0 + kx;
+        const bool inside = k + i < K && (unsigned)y < (unsigned)g.H && (unsigned)xx < (unsigned)g.W;
+        e[i] = inside ? __ldg(x + (((size_t)n * g.C + c) * g.H + y) * g.W + xx) : 0.0f;
+        if (++kx == g.KW) { kx = 0; if (++ky == g.KH) { ky = 0; ++c; } }
+    }
+    return make_float4(e[0], e[1], e[2], e[3]);
+}
+
 struct WindowsOfImage {      // forward: b = image, r = window (oy, ox) of that image, k = position
     const float* x; ConvGeom g;
     __device__ __forceinline__ float at(int b, int r, int k) const {
         const int oy = g.by_ow.div(r);
         return conv_window_value(x, g, b, oy, r - oy * g.OW, k);
     }
-    RGB_QUAD_BY_ELEMENTS
+    __device__ __forceinline__ float4 quad(int b, int r, int k, int K) const {
+        const int oy = g.by_ow.div(r);
+        return conv_window_quad(x, g, b, oy, r - oy * g.OW, k, K);
+    }
 };
 
 struct AllWindows {          // forward: r = window (n, oy, ox) over all images, k = position
@@ -97,7 +117,11 @@ struct AllWindows {          // forward: r = window (n, oy, ox) over all images,
         const int oy = g.by_ow.div(j);
         return conv_window_value(x, g, n, oy, j - oy * g.OW, k);
     }
-    RGB_QUAD_BY_ELEMENTS
+    __device__ __forceinline__ float4 quad(int, int r, int k, int K) const {
+        const int n = g.by_per.div(r), j = r - n * (g.OH * g.OW);
+        const int oy = g.by_ow.div(j);
+        return conv_window_quad(x, g, n, oy, j - oy * g.OW, k, K);
+    }
 };
 
 struct PositionsOverWindows {   // weight gradient: r = position, k = window (n, oy, ox)
@@ -107,7 +131,22 @@ struct PositionsOverWindows {   // weight gradient: r = position, k = window (n,
         const int oy = g.by_ow.div(j);
         return conv_window_value(x, g, n, oy, j - oy * g.OW, r);
     }
-    RGB_QUAD_BY_ELEMENTS
+    __device__ __forceinline__ float4 quad(int, int r, int k, int K) const {   // four consecutive windows, one position
+        const int c = g.by_khw.div(r), rem = r - c * (g.KH * g.KW);
+        const int ky = g.by_kw.div(rem), kx = rem - ky * g.KW;
+        int n = g.by_per.div(k);
+        const int j = k - n * (g.OH * g.OW);
+        int oy = g.by_ow.div(j), ox = j - oy * g.OW;
+        float e[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int y = oy * g.SY - g.PY + ky, xx = ox * g.SX - g.PX + kx;
+            const bool inside = k + i < K && (unsigned)y < (unsigned)g.H && (unsigned)xx < (unsigned)g.W;
+            e[i] = inside ? __ldg(x + (((size_t)n * g.C + c) * g.H + y) * g.W + xx) : 0.0f;
+            if (++ox == g.OW) { ox = 0; if (++oy == g.OH) { oy = 0; ++n; } }
+        }
+        return make_float4(e[0], e[1], e[2], e[3]);
+    }
 };
 
 struct FiltersOverWindows {     // weight gradient: r = filter, k = window (n, oy, ox); dY is [N][F][OH*OW]
@@ -117,7 +156,13 @@ struct FiltersOverWindows {     // weight gradient: r = filter, k = window (n, o
         const int n = g.by_per.div(k), j = k - n * per;
         return __ldg(dy + ((size_t)n * g.F + r) * per + j);
     }
-    RGB_QUAD_BY_ELEMENTS
+    __device__ __forceinline__ float4 quad(int b, int r, int k, int K) const {   // contiguous within an image
+        const int per = g.OH * g.OW;
+        const int n = g.by_per.div(k), j = k - n * per;
+        if (k + 3 >= K || j + 3 >= per) return quad_by_elements(*this, b, r, k, K);
+        const float* p = dy + ((size_t)n * g.F + r) * per + j;
+        return make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+    }
 };
 
 // Input gradient: the index k runs over (ky, kx, f) with the filter f fastest (any order gives the same
@@ -150,13 +195,23 @@ struct PixelsOverTaps {         // b = image, r = pixel (y, x), k = (tap, f)
         return p ? __ldg(p + (size_t)f * (g.OH * g.OW)) : 0.0f;
     }
     __device__ __forceinline__ float4 quad(int b, int r, int k, int K) const {
+        if (g.F < 4) return quad_by_elements(*this, b, r, k, K);        // a quad could span three taps
+        if (k >= K) return make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        // elements 0 .. first-1 are filters f .. of this tap, the rest filters 0 .. of the next tap (none after the last)
         const int tap = g.by_f.div(k), f = k - tap * g.F;
-        if (k >= K || f + 3 >= g.F) return quad_by_elements(*this, b, r, k, K);   // straddles two taps or the end
-        const float* p = window_at_tap(b, r, tap);
-        if (!p) return make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const int first = min(4, g.F - f);
         const size_t per = (size_t)g.OH * g.OW;
-        p += f * per;
-        return make_float4(__ldg(p), __ldg(p + per), __ldg(p + 2 * per), __ldg(p + 3 * per));
+        const float* p0 = window_at_tap(b, r, tap);
+        const float* p1 = (first < 4 && tap + 1 < g.KH * g.KW) ? window_at_tap(b, r, tap + 1) : nullptr;
+        if (p0) p0 += f * per;
+        if (p1) p1 -= first * per;                                      // so that element i reads p1 + i * per
+        float e[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float* p = i < first ? p0 : p1;
+            e[i] = p ? __ldg(p + i * per) : 0.0f;
+        }
+        return make_float4(e[0], e[1], e[2], e[3]);
     }
 };
 
@@ -199,7 +254,7 @@ gather_max_kernel(const Source src, uint32_t* __restrict__ maxbits, int R, int K
     if (row >= R) return;
     const int k_lo = blockIdx.y * GATHER_CHUNK, k_hi = min(K, k_lo + GATHER_CHUNK);
     float m = 0.0f;
-    for (int k = k_lo + lane; k < k_hi; k += 32) m = fmaxf(m, fabsf(src.at(b, row, k)));
+    for (int k = k_lo + lane * 4; k < k_hi; k += 128) m = abs4max(m, src.quad(b, row, k, K));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
     if (lane == 0 && m > 0.0f) atomicMax(maxbits + (size_t)b * slot_batch_mul + (size_t)row * slot_row_mul, f32_bits(m));
