@@ -102,3 +102,27 @@ def test_reference_conv_test_program_passes_against_this_library():
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "OVERALL: PASS" in res.stdout and "FAIL " not in res.stdout
     assert res.stdout.count("  ok ") == 36
+
+
+def test_conv2d_layer_autograd_matches_oracle():
+    """The torch layer: forward, input gradient and weight gradient through autograd equal the oracle's three
+    results; a bias adds one IEEE addition per output."""
+    from bit_reproducible_training_b200 import layers
+    shape = (3, 5, 11, 9, 12, 3, 3, 1, 2, 1, 0)
+    N, C, H, W, F, KH, KW, SY, SX, PY, PX = shape
+    x, w, dy = fx.conv_inputs(shape)
+    layer = layers.Conv2d(C, F, (KH, KW), stride=(SY, SX), padding=(PY, PX), bias=True).cuda()
+    bias = torch.linspace(-1.0, 1.0, F)
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(w).reshape(F, C, KH, KW))
+        layer.bias.copy_(bias)
+    layer.bias.requires_grad_(False)
+    xin = torch.from_numpy(x).reshape(N, C, H, W).cuda().requires_grad_(True)
+    y = layer(xin)
+    want = torch.from_numpy(oracle.conv2d(x, w, shape, 3)) + bias[None, :, None, None]
+    assert np.array_equal(bits(y), want.numpy().reshape(-1).view(np.uint32))
+    y.backward(torch.from_numpy(dy).reshape(y.shape).cuda())
+    assert np.array_equal(bits(xin.grad), oracle.conv2d_grad_input(dy, w, shape, 3).reshape(-1).view(np.uint32))
+    assert np.array_equal(bits(layer.weight.grad), oracle.conv2d_grad_weight(dy, x, shape, 3).reshape(-1).view(np.uint32))
+    with pytest.raises(NotImplementedError):
+        layers.Conv2d(C, F, 3, dilation=2).cuda()(xin)
