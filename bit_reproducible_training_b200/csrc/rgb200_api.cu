@@ -517,7 +517,12 @@ cudaError_t conv_layout(ConvKind kind, const ConvGeom& g, int S, Layout& L) {
     return cudaErrorInvalidValue;
 }
 
-struct ConvCall { ConvKind kind; ConvGeom g; const float* p; const float* q; bool places; };   // (x, weight), (dy, x) or (dy, weight)
+// (p, q) = (x, weight), (dy, x) or (dy, weight); pixmax: C*H*W words behind the product's workspace (weight gradient)
+struct ConvCall { ConvKind kind; ConvGeom g; const float* p; const float* q; bool places; uint32_t* pixmax; };
+
+size_t conv_extra_bytes(ConvKind kind, const ConvGeom& g) {
+    return kind == CONV_GRAD_WEIGHT ? align_up((size_t)g.C * g.H * g.W * sizeof(uint32_t)) : 0;
+}
 
 cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint32_t* max_b, int8_t* qa, int8_t* qb,
                          int* ea, int* eb, cudaStream_t st) {
@@ -526,31 +531,52 @@ cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint
     const int S = L.S;
     const FastDiv one;
     switch (c.kind) {
-        case CONV_FORWARD:
-            if (c.places) {           // A: every window of every image; B: the weights as stored
-                launch_gather_operand(S, AllWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
-                launch_gather_operand(S, StoredRows{c.q, g.K}, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+        case CONV_FORWARD: {
+            // k runs (tap, channel) when there are at least four channels, else (c, ky, kx) as the weights are stored
+            const bool tap_major = g.C >= 4;
+            const size_t khw = (size_t)g.KH * g.KW;
+            const TapMajorWeights wt{c.q, g, g.C, g.by_c, (size_t)g.C * khw, khw};
+            const StoredRows ws{c.q, g.K};
+            if (c.places) {           // A: every window of every image; B: the weights
+                if (tap_major) {
+                    launch_gather_operand(S, AllWindowTaps{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
+                    launch_gather_operand(S, wt, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+                } else {
+                    launch_gather_operand(S, AllWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
+                    launch_gather_operand(S, ws, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+                }
             } else {                  // per image: A the weights (one copy of the planes per image), B the windows of image b
-                launch_gather_operand(S, StoredRows{c.q, g.K}, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, one, st);
-                launch_gather_operand(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                if (tap_major) {
+                    launch_gather_operand(S, wt, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                    launch_gather_operand(S, WindowTapsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                } else {
+                    launch_gather_operand(S, ws, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                    launch_gather_operand(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                }
             }
             break;
+        }
         case CONV_GRAD_WEIGHT:        // A: dY by filter over all windows; B: window values by position over all windows
             launch_gather_operand(S, FiltersOverWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
-            launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+            // the position maxima come from a per-pixel maximum over the images instead of a second gather
+            pixel_max_over_images_kernel<<<dim3(ceil_div(g.H * g.W, PREPASS_THREADS), g.C < 65535 ? g.C : 65535), PREPASS_THREADS, 0, st>>>(
+                c.q, c.pixmax, g.N, g.C, g.H * g.W);
+            position_max_kernel<<<ceil_div(g.K, PREPASS_THREADS / 32), PREPASS_THREADS, 0, st>>>(c.pixmax, max_b, g);
+            launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 1, one, st);
             break;
-        case CONV_GRAD_INPUT: {       // dY taps per pixel with one scale per image; weights by input channel with one scale for all
+        case CONV_GRAD_INPUT: {       // k runs (tap, filter); dY taps per pixel with one scale per image, weights by channel with one scale
             uint32_t* max_w = c.places ? max_b : max_a;
             uint32_t* max_img = c.places ? max_a : max_b;     // N words: both regions hold at least N (rows >= N, batch >= N)
+            const size_t khw = (size_t)g.KH * g.KW;
+            const TapMajorWeights wt{c.q, g, g.F, g.by_f, khw, (size_t)g.C * khw};
             launch_gather_max(StoredRows{c.q, (long long)g.F * g.K}, max_w, 1, g.F * g.K, 1, 0, 0, st);
             launch_gather_max(StoredRows{c.p, (long long)g.F * g.OH * g.OW}, max_img, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
             if (c.places) {
-                launch_gather_operand(S, AllPixelsOverTaps{c.p, g, FastDiv(g.H * g.W)}, max_img, qa, ea, L.M, L.K, L.Kp, 1, false, 0, 1,
-                                      FastDiv(g.H * g.W), st);
-                launch_gather_operand(S, ChannelsOverTaps{c.q, g}, max_w, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 0, one, st);
+                launch_gather_operand(S, AllPixelTaps{c.p, g}, max_img, qa, ea, L.M, L.K, L.Kp, 1, false, 0, 1, g.by_hw, st);
+                launch_gather_operand(S, wt, max_w, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 0, one, st);
             } else {
-                launch_gather_operand(S, ChannelsOverTaps{c.q, g}, max_w, qa, ea, L.M, L.K, L.Kp, L.batch, false, 0, 0, one, st);
-                launch_gather_operand(S, PixelsOverTaps{c.p, g}, max_img, qb, eb, L.N, L.K, L.Kp, L.batch, false, 1, 0, one, st);
+                launch_gather_operand(S, wt, max_w, qa, ea, L.M, L.K, L.Kp, L.batch, false, 0, 0, one, st);
+                launch_gather_operand(S, PixelTapsOfImage{c.p, g}, max_img, qb, eb, L.N, L.K, L.Kp, L.batch, false, 1, 0, one, st);
             }
             break;
         }
@@ -563,7 +589,7 @@ cudaError_t conv_workspace(ConvKind kind, const rgb200_conv_shape* shape, int S,
     if (!bytes || !conv_geometry(shape, S, g)) return cudaErrorInvalidValue;
     Layout L;
     cudaError_t e = conv_layout(kind, g, S, L);
-    if (e == cudaSuccess) *bytes = L.total;
+    if (e == cudaSuccess) *bytes = L.total + conv_extra_bytes(kind, g);
     return e;
 }
 
@@ -574,10 +600,11 @@ cudaError_t conv_run(ConvKind kind, const float* p, const float* q, float* out, 
     Layout L;
     cudaError_t e = conv_layout(kind, g, S, L);
     if (e != cudaSuccess) return e;
-    if (!p || !q || !out || !ws || ws_bytes < L.total) return cudaErrorInvalidValue;
+    if (!p || !q || !out || !ws || ws_bytes < L.total + conv_extra_bytes(kind, g)) return cudaErrorInvalidValue;
     const DeviceInfo* dev = nullptr;
     if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
-    const ConvCall call{kind, g, p, q, conv_rows_are_places(kind, g, S)};
+    const ConvCall call{kind, g, p, q, conv_rows_are_places(kind, g, S),
+                        reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + L.total)};
     const PrepassHook hook{conv_prepass, &call};
     RunArgs a{nullptr, nullptr, out, nullptr, nullptr, nullptr, 0, 0, (long long)L.M * L.N, false, true,
               static_cast<char*>(ws), static_cast<cudaStream_t>(stream), nullptr};
