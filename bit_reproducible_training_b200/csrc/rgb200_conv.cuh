@@ -138,7 +138,11 @@ __device__ __forceinline__ void tap_major_hex(const Lookup& lookup, int I, FastD
         v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
     }
 }
+// kSixteenPerLane: whether the long-row kernels fetch sixteen consecutive k per lane (sources whose consecutive
+// k lie a plane apart: nothing to coalesce, fewer index computations) or four (sources whose consecutive k are
+// consecutive in memory: a warp's loads then cover contiguous 512 bytes).
 #define RGB_TAP_MAJOR(I_, BY_I_, STRIDE_, LOOKUP_)                                                                   \
+    static constexpr bool kSixteenPerLane = true;                                                                    \
     __device__ __forceinline__ float at(int b, int r, int k) const {                                                 \
         return tap_major_at(LOOKUP_, I_, BY_I_, STRIDE_, k);                                                         \
     }                                                                                                                \
@@ -213,6 +217,7 @@ __device__ __forceinline__ float4 conv_window_quad(const float* __restrict__ x, 
     return make_float4(e[0], e[1], e[2], e[3]);
 }
 struct WindowsOfImage {         // b = image, r = window (oy, ox) of that image, k = position
+    static constexpr bool kSixteenPerLane = false;
     const float* x; ConvGeom g;
     __device__ __forceinline__ float at(int b, int r, int k) const {
         const int oy = g.by_ow.div(r);
@@ -225,6 +230,7 @@ struct WindowsOfImage {         // b = image, r = window (oy, ox) of that image,
     RGB_HEX_BY_QUADS
 };
 struct AllWindows {             // r = window (n, oy, ox) over all images, k = position
+    static constexpr bool kSixteenPerLane = false;
     const float* x; ConvGeom g;
     __device__ __forceinline__ float at(int, int r, int k) const {
         const int n = g.by_per.div(r), j = r - n * (g.OH * g.OW);
@@ -241,6 +247,7 @@ struct AllWindows {             // r = window (n, oy, ox) over all images, k = p
 
 // ---- weight gradient: k = window (n, oy, ox) ----
 struct PositionsOverWindows {   // r = position (c, ky, kx)
+    static constexpr bool kSixteenPerLane = false;
     const float* x; ConvGeom g;
     __device__ __forceinline__ float at(int, int r, int k) const {
         const int n = g.by_per.div(k), j = k - n * (g.OH * g.OW);
@@ -280,6 +287,7 @@ struct PositionsOverWindows {   // r = position (c, ky, kx)
     __device__ __forceinline__ void hex(int, int r, int k, int K, float (&v)[16]) const { run<16>(r, k, K, v); }
 };
 struct FiltersOverWindows {     // r = filter; dY is [N][F][OH*OW]: contiguous within an image
+    static constexpr bool kSixteenPerLane = false;
     const float* dy; ConvGeom g;
     __device__ __forceinline__ float at(int, int r, int k) const {
         const int per = g.OH * g.OW;
@@ -320,6 +328,7 @@ struct AllPixelTaps {           // r = pixel (n, y, x) over all images
 };
 
 struct StoredRows {             // a stored matrix [R][K] (the weights as they are; whole tensors for their maxima)
+    static constexpr bool kSixteenPerLane = false;
     const float* src; long long row_len;
     __device__ __forceinline__ float at(int, int r, int k) const { return __ldg(src + (size_t)r * row_len + k); }
     RGB_QUAD_BY_ELEMENTS
@@ -424,10 +433,14 @@ gather_max_kernel(const Source src, uint32_t* __restrict__ maxbits, int R, int K
     if (row >= R) return;
     const int k_lo = blockIdx.y * GATHER_CHUNK, k_hi = min(K, k_lo + GATHER_CHUNK);
     float m = 0.0f;
-    for (int k = k_lo + lane * 16; k < k_hi; k += 512) {
-        float v[16];
-        src.hex(b, row, k, K, v);
-        m = abs16max(m, v);
+    if (Source::kSixteenPerLane) {
+        for (int k = k_lo + lane * 16; k < k_hi; k += 512) {
+            float v[16];
+            src.hex(b, row, k, K, v);
+            m = abs16max(m, v);
+        }
+    } else {
+        for (int k = k_lo + lane * 4; k < k_hi; k += 128) m = abs4max(m, src.quad(b, row, k, K));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
@@ -449,10 +462,15 @@ gather_split_kernel(const Source src, const uint32_t* __restrict__ maxbits, int8
     const size_t plane_stride = (size_t)R * Kp;
     int8_t* out = planes + (size_t)b * S * plane_stride + (size_t)row * Kp;
     const int k_lo = blockIdx.y * GATHER_CHUNK, k_hi = min(Kp, k_lo + GATHER_CHUNK);
-    for (int k = k_lo + lane * 16; k < k_hi; k += 512) {         // a warp writes 512 contiguous bytes per plane
-        float v[16];
-        src.hex(b, row, k, K, v);                                // zeros from K up to Kp
-        store_hex<S>(v, q, plain, out, plane_stride, (size_t)k);
+    if (Source::kSixteenPerLane) {
+        for (int k = k_lo + lane * 16; k < k_hi; k += 512) {     // a warp writes 512 contiguous bytes per plane
+            float v[16];
+            src.hex(b, row, k, K, v);                            // zeros from K up to Kp
+            store_hex<S>(v, q, plain, out, plane_stride, (size_t)k);
+        }
+    } else {
+        for (int k = k_lo + lane * 4; k < k_hi; k += 128)        // a warp writes 128 contiguous bytes per plane
+            store_quad<S>(src.quad(b, row, k, K), q, plain, out, plane_stride, (size_t)k);
     }
 }
 
