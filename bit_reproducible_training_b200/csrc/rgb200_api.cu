@@ -561,7 +561,7 @@ cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint
             // the position maxima come from a per-pixel maximum over the images instead of a second gather
             pixel_max_over_images_kernel<<<dim3(ceil_div(g.H * g.W, PREPASS_THREADS), g.C < 65535 ? g.C : 65535), PREPASS_THREADS, 0, st>>>(
                 c.q, c.pixmax, g.N, g.C, g.H * g.W);
-            position_max_kernel<<<ceil_div(g.K, PREPASS_THREADS / 32), PREPASS_THREADS, 0, st>>>(c.pixmax, max_b, g);
+            position_max_kernel<<<g.K, PREPASS_THREADS, 0, st>>>(c.pixmax, max_b, g);
             launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 1, one, st);
             break;
         case CONV_GRAD_INPUT: {       // k runs (tap, filter); dY taps per pixel with one scale per image, weights by channel with one scale

@@ -362,20 +362,18 @@ pixel_max_over_images_kernel(const float* __restrict__ x, uint32_t* __restrict__
 
 __global__ void __launch_bounds__(PREPASS_THREADS)
 position_max_kernel(const uint32_t* __restrict__ pixmax, uint32_t* __restrict__ maxbits, const ConvGeom g) {
-    const int lane = threadIdx.x & 31;
-    const int pos = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5);     // grid = ceil(K / 8), one warp per position
-    if (pos >= g.K) return;
+    const int pos = blockIdx.x;                                     // grid = K, one CTA per position; maxbits zero on entry
     const int c = g.by_khw.div(pos), rem = pos - c * (g.KH * g.KW);
     const int ky = g.by_kw.div(rem), kx = rem - ky * g.KW;
     uint32_t m = 0u;
-    for (int j = lane; j < g.OH * g.OW; j += 32) {
+    for (int j = threadIdx.x; j < g.OH * g.OW; j += PREPASS_THREADS) {
         const int oy = g.by_ow.div(j), ox = j - oy * g.OW;
         const int y = oy * g.SY - g.PY + ky, xx = ox * g.SX - g.PX + kx;
         if ((unsigned)y < (unsigned)g.H && (unsigned)xx < (unsigned)g.W) m = max(m, pixmax[((size_t)c * g.H + y) * g.W + xx]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if (lane == 0) maxbits[pos] = m;
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(maxbits + pos, m);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -480,8 +478,7 @@ gather_split_kernel(const Source src, const uint32_t* __restrict__ maxbits, int8
 // the scale comes from a maximum reduced beforehand (shared by several rows).
 //   gather_rows_kernel      four k per lane; rows of at most 32 or 64 values take 8 or 16 lanes (4 or 2 rows
 //                           per warp) and fill the rest of the 128-byte plane row with 16-byte zero stores
-//   gather_rows16_kernel    sixteen k per lane and step (HEXES steps): Kp = 128 takes 8 lanes, 256 takes 16,
-//                           up to 512 takes 32 lanes, up to 1024 two steps
+//   gather_rows16_kernel    sixteen k per lane and step (HEXES steps), 8, 16 or 32 lanes per row
 // grid = (ceil(R / (8 * 32 / LANES)), 1, batch), 256 threads
 // ---------------------------------------------------------------------------------------------
 template <int S, class Source, int LANES, bool OWN_MAX>
@@ -520,7 +517,6 @@ template <int S, class Source, int HEXES, int LANES, bool OWN_MAX>
 __global__ void __launch_bounds__(PREPASS_THREADS)
 gather_rows16_kernel(const Source src, const uint32_t* __restrict__ maxbits, int8_t* __restrict__ planes,
                      int* __restrict__ expo, int R, int K, int Kp, int slot_batch_mul, int slot_row_mul, FastDiv slot_div) {
-    static_assert(LANES == 32 || HEXES == 1, "narrow row groups take one step");
     constexpr int ROWS_PER_WARP = 32 / LANES;
     const int lane = threadIdx.x & 31, sub = lane % LANES;
     const int row = (blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5)) * ROWS_PER_WARP + lane / LANES;
@@ -563,9 +559,12 @@ void launch_gather_rows_s(const Source& src, const uint32_t* maxbits, int8_t* pl
 #define RGB_ARGS src, maxbits, planes, expo, R, K, Kp, slot_batch_mul, slot_row_mul, slot_div
     if (K <= 32) gather_rows_kernel<S, Source, 8, OWN_MAX><<<RGB_GRID(8)>>>(RGB_ARGS);
     else if (K <= 64) gather_rows_kernel<S, Source, 16, OWN_MAX><<<RGB_GRID(16)>>>(RGB_ARGS);
+    // lanes per row x steps chosen so that few lanes idle: 8, 16, 24, 32, 48 and 64 sixteens per row fit exactly
     else if (Kp <= 128) gather_rows16_kernel<S, Source, 1, 8, OWN_MAX><<<RGB_GRID(8)>>>(RGB_ARGS);
     else if (Kp <= 256) gather_rows16_kernel<S, Source, 1, 16, OWN_MAX><<<RGB_GRID(16)>>>(RGB_ARGS);
+    else if (Kp <= 384) gather_rows16_kernel<S, Source, 3, 8, OWN_MAX><<<RGB_GRID(8)>>>(RGB_ARGS);
     else if (Kp <= 512) gather_rows16_kernel<S, Source, 1, 32, OWN_MAX><<<RGB_GRID(32)>>>(RGB_ARGS);
+    else if (Kp <= 768) gather_rows16_kernel<S, Source, 3, 16, OWN_MAX><<<RGB_GRID(16)>>>(RGB_ARGS);
     else gather_rows16_kernel<S, Source, 2, 32, OWN_MAX><<<RGB_GRID(32)>>>(RGB_ARGS);
 #undef RGB_GRID
 #undef RGB_ARGS
