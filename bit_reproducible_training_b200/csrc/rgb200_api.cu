@@ -539,30 +539,30 @@ cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint
             const StoredRows ws{c.q, g.K};
             if (c.places) {           // A: every window of every image; B: the weights
                 if (tap_major) {
-                    launch_gather_operand(S, AllWindowTaps{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
-                    launch_gather_operand(S, wt, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+                    launch_gather_operand<true>(S, AllWindowTaps{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, 0, 0, one, st);
+                    launch_gather_operand<true>(S, wt, max_b, qb, eb, L.N, L.K, L.Kp, 1, 0, 0, one, st);
                 } else {
-                    launch_gather_operand(S, AllWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
-                    launch_gather_operand(S, ws, max_b, qb, eb, L.N, L.K, L.Kp, 1, true, 0, 0, one, st);
+                    launch_gather_operand<true>(S, AllWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, 0, 0, one, st);
+                    launch_gather_operand<true>(S, ws, max_b, qb, eb, L.N, L.K, L.Kp, 1, 0, 0, one, st);
                 }
             } else {                  // per image: A the weights (one copy of the planes per image), B the windows of image b
                 if (tap_major) {
-                    launch_gather_operand(S, wt, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, one, st);
-                    launch_gather_operand(S, WindowTapsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                    launch_gather_operand<true>(S, wt, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 0, one, st);
+                    launch_gather_operand<true>(S, WindowTapsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, 0, 0, one, st);
                 } else {
-                    launch_gather_operand(S, ws, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, true, 0, 0, one, st);
-                    launch_gather_operand(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, true, 0, 0, one, st);
+                    launch_gather_operand<true>(S, ws, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 0, one, st);
+                    launch_gather_operand<true>(S, WindowsOfImage{c.p, g}, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, 0, 0, one, st);
                 }
             }
             break;
         }
         case CONV_GRAD_WEIGHT:        // A: dY by filter over all windows; B: window values by position over all windows
-            launch_gather_operand(S, FiltersOverWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, true, 0, 0, one, st);
+            launch_gather_operand<true>(S, FiltersOverWindows{c.p, g}, max_a, qa, ea, L.M, L.K, L.Kp, 1, 0, 0, one, st);
             // the position maxima come from a per-pixel maximum over the images instead of a second gather
             pixel_max_over_images_kernel<<<dim3(ceil_div(g.H * g.W, PREPASS_THREADS), g.C < 65535 ? g.C : 65535), PREPASS_THREADS, 0, st>>>(
                 c.q, c.pixmax, g.N, g.C, g.H * g.W);
             position_max_kernel<<<g.K, PREPASS_THREADS, 0, st>>>(c.pixmax, max_b, g);
-            launch_gather_operand(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 1, one, st);
+            launch_gather_operand<false>(S, PositionsOverWindows{c.q, g}, max_b, qb, eb, L.N, L.K, L.Kp, 1, 0, 1, one, st);
             break;
         case CONV_GRAD_INPUT: {       // k runs (tap, filter); dY taps per pixel with one scale per image, weights by channel with one scale
             uint32_t* max_w = c.places ? max_b : max_a;
@@ -572,11 +572,11 @@ cudaError_t conv_prepass(const void* ctx, const Layout& L, uint32_t* max_a, uint
             launch_gather_max(StoredRows{c.q, (long long)g.F * g.K}, max_w, 1, g.F * g.K, 1, 0, 0, st);
             launch_gather_max(StoredRows{c.p, (long long)g.F * g.OH * g.OW}, max_img, g.N, g.F * g.OH * g.OW, 1, 0, 1, st);
             if (c.places) {
-                launch_gather_operand(S, AllPixelTaps{c.p, g}, max_img, qa, ea, L.M, L.K, L.Kp, 1, false, 0, 1, g.by_hw, st);
-                launch_gather_operand(S, wt, max_w, qb, eb, L.N, L.K, L.Kp, 1, false, 0, 0, one, st);
+                launch_gather_operand<false>(S, AllPixelTaps{c.p, g}, max_img, qa, ea, L.M, L.K, L.Kp, 1, 0, 1, g.by_hw, st);
+                launch_gather_operand<false>(S, wt, max_w, qb, eb, L.N, L.K, L.Kp, 1, 0, 0, one, st);
             } else {
-                launch_gather_operand(S, wt, max_w, qa, ea, L.M, L.K, L.Kp, L.batch, false, 0, 0, one, st);
-                launch_gather_operand(S, PixelTapsOfImage{c.p, g}, max_img, qb, eb, L.N, L.K, L.Kp, L.batch, false, 1, 0, one, st);
+                launch_gather_operand<false>(S, wt, max_w, qa, ea, L.M, L.K, L.Kp, L.batch, 0, 0, one, st);
+                launch_gather_operand<false>(S, PixelTapsOfImage{c.p, g}, max_img, qb, eb, L.N, L.K, L.Kp, L.batch, 1, 0, one, st);
             }
             break;
         }

@@ -588,26 +588,22 @@ void launch_gather_split(int S, const Source& src, const uint32_t* maxbits, int8
     }
 }
 
-// One operand through the gather pre-pass.  own_max: every row has its own scale (its slot is
+// One operand through the gather pre-pass.  OWN_MAX: every row has its own scale (its slot is
 // b * R + r); otherwise the maxima were reduced beforehand into the given slots.
-template <class Source>
+template <bool OWN_MAX, class Source>
 void launch_gather_operand(int S, const Source& src, uint32_t* maxbits, int8_t* planes, int* expo, int R, int K, int Kp,
-                           int batch, bool own_max, int slot_batch_mul, int slot_row_mul, FastDiv slot_div, cudaStream_t st) {
+                           int batch, int slot_batch_mul, int slot_row_mul, FastDiv slot_div, cudaStream_t st) {
+    if (OWN_MAX) { slot_batch_mul = R; slot_row_mul = 1; slot_div = FastDiv(); }
     if (Kp > GATHER_ROWS_MAX_KP) {             // long rows: maxima by atomics over chunks, then the split
-        if (own_max) {
-            slot_batch_mul = R; slot_row_mul = 1; slot_div = FastDiv();
-            launch_gather_max(src, maxbits, R, K, batch, slot_batch_mul, slot_row_mul, st);
-        }
+        if (OWN_MAX) launch_gather_max(src, maxbits, R, K, batch, slot_batch_mul, slot_row_mul, st);
         launch_gather_split(S, src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, slot_div, st);
         return;
     }
-#define RGB_OPERAND(SS)                                                                                                  \
-    do {                                                                                                                 \
-        if (own_max) launch_gather_rows_s<SS, Source, true>(src, maxbits, planes, expo, R, K, Kp, batch, 0, 0, FastDiv(), st); \
-        else launch_gather_rows_s<SS, Source, false>(src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, slot_div, st); \
-    } while (0)
-    if (S == 1) RGB_OPERAND(1); else if (S == 2) RGB_OPERAND(2); else RGB_OPERAND(3);
-#undef RGB_OPERAND
+    switch (S) {
+        case 1: launch_gather_rows_s<1, Source, OWN_MAX>(src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, slot_div, st); break;
+        case 2: launch_gather_rows_s<2, Source, OWN_MAX>(src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, slot_div, st); break;
+        default: launch_gather_rows_s<3, Source, OWN_MAX>(src, maxbits, planes, expo, R, K, Kp, batch, slot_batch_mul, slot_row_mul, slot_div, st); break;
+    }
 }
 
 }  // namespace rgb200
