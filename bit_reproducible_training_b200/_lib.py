@@ -66,6 +66,7 @@ def lib():
     L.rgb200_fixed_point.argtypes = [C.c_float, i, i]
     L.rgb200_round_to_float_bits.argtypes = [ll, i]
     L.rgb200_round_to_float_bits.restype = C.c_uint32
+    L.rgb200_fast_div.argtypes = [i, i]
     L.rgb200_layout.argtypes = [i, i, i, i, cfgp, C.POINTER(LayoutInfo)]
     shp = C.POINTER(ConvShape)
     for name in ("rgb200_conv2d", "rgb200_conv2d_grad_weight", "rgb200_conv2d_grad_input"):

@@ -677,6 +677,11 @@ const char* rgb200_algo_name(int algo) {
     return "?";
 }
 
+int rgb200_fast_div(int divisor, int n) {
+    if (divisor < 1 || n < 0) return -1;
+    return FastDiv(divisor).div(n);
+}
+
 int rgb200_layout(int M, int N, int K, int batch, const rgb200_config* cfg, rgb200_layout_info* info) {
     if (!cfg || !info) return cudaErrorInvalidValue;
     Layout L;

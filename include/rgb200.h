@@ -206,6 +206,9 @@ uint64_t rgb200_fnv1a64(const void* data, size_t bytes, uint64_t h);
 int rgb200_scale_exponent(float absmax);
 int rgb200_fixed_point(float x, int scale_exponent, int slices);
 uint32_t rgb200_round_to_float_bits(long long T, int E);
+/* floor(n / divisor) for 0 <= n < 2^31 and divisor >= 1 by the multiply-high form the convolution index maps
+ * use on the device (same constants, host arithmetic), so the form can be checked without a GPU. */
+int rgb200_fast_div(int divisor, int n);
 
 /* Pure host planning (no device query): padded K, number of 128-wide K blocks, the K-range count
  * the INT32 accumulators force, and the workspace size, for tests and capacity planning.

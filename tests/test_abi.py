@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(L):
     header = open(os.path.join(ROOT, "include", "rgb200.h")).read()
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
     names = set(re.findall(r"\b(rgb200_[a-z0-9_]+)\s*\(", header))
-    assert len(names) >= 23
+    assert len(names) >= 24
     for n in sorted(names):
         assert hasattr(L, n), "librgb200.so does not export %s" % n
 
@@ -65,6 +65,24 @@ def test_conv_workspace_planning_and_shape_checks(L):
     # more windows than an exact INT64 sum allows at S = 3 (9e18 / (127 * 128^2)^2 = 2 078 698)
     assert rc.conv2d_grad_weight_workspace(rc.ConvShape(600, 1, 60, 60, 4, 1, 1), 3)[0] == rg.cudaErrorInvalidValue
     assert rc.conv2d_grad_weight_workspace(rc.ConvShape(600, 1, 60, 60, 4, 1, 1), 2)[0] == 0
+
+
+def test_index_division_by_multiply_high_is_exact(L):
+    """The convolutions' index maps divide by kernel and image extents with one multiply-high and a shift;
+    the library's host copy of that arithmetic must equal floor division for every n below 2^31."""
+    rng = np.random.default_rng(11)
+    divisors = list(range(1, 300)) + [int(v) for v in rng.integers(1, 1 << 31, size=300)] + \
+        [(1 << k) + j for k in range(1, 31) for j in (-1, 0, 1)] + [(1 << 31) - 1]
+    for d in divisors:
+        if d < 1:
+            continue
+        top = (1 << 31) - 1
+        ns = [0, 1, d - 1, d, d + 1, 2 * d - 1, 2 * d, top, top - 1, (top // d) * d, (top // d) * d - 1]
+        ns += [int(v) for v in rng.integers(0, 1 << 31, size=40)]
+        for n in ns:
+            if 0 <= n <= top:
+                assert L.rgb200_fast_div(d, n) == n // d, (d, n)
+    assert L.rgb200_fast_div(0, 5) == -1 and L.rgb200_fast_div(3, -1) == -1
 
 
 def test_default_config_matches_reference_defaults(L):
