@@ -277,6 +277,11 @@ CONV_CASES = [
     ("wide.range", (3, 5, 11, 9, 12, 3, 3, 1, 2, 1, 0), "wide"),
     # enough windows that the weight gradient is cut into several accumulation ranges
     ("many.windows", (64, 3, 48, 48, 8, 3, 3, 1, 1, 1, 1), "normal"),
+    # row lengths that take the remaining lane layouts of the one-launch pre-pass (padded K of 512, 640 and 768)
+    ("k432", (1, 48, 6, 6, 8, 3, 3, 1, 1, 1, 1), "normal"),
+    ("k576.window", (2, 64, 8, 8, 24, 3, 3, 1, 1, 1, 1), "normal"),
+    ("k576.taps", (2, 8, 8, 8, 64, 3, 3, 1, 1, 1, 1), "wide"),
+    ("k700", (1, 28, 7, 9, 76, 5, 5, 2, 1, 2, 2), "normal"),
     # more than 105 472 values per window / taps per pixel: the forward (first) and the input gradient
     # (second) need several INT32 accumulation passes at S = 3 and take the one-product-per-image form
     ("long.window", (2, 300, 19, 19, 2, 19, 19, 1, 1, 9, 9), "normal"),
