@@ -233,3 +233,42 @@ def test_cxx_caller_builds_against_the_shim_and_links_the_library(L, tmp_path):
         assert int(out[0]) != 0                    # no device: an error code, not a crash
     assert int(out[1]) == rg.cudaErrorInvalidValue and int(out[2]) == rg.cudaErrorNotSupported
     assert out[3:] == ["tc", "ref", "3"]
+
+
+CXX_CONV_CALLER = r"""
+// A caller written against the reference's convolution surface (repro_conv_cuda/repro_conv.cuh:22-32).
+#include "repro_conv.cuh"
+#include <cstdio>
+int main() {
+    repro_conv::ConvShape g;                      // stride 1 and no padding by default, as in the reference
+    g.N = 100; g.C = 1; g.H = 28; g.W = 28; g.F = 6; g.KH = 5; g.KW = 5; g.PY = 2; g.PX = 2;
+    size_t b0 = 0, b1 = 0, b2 = 0;
+    cudaError_t e0 = repro_conv::conv2d_workspace(g, 3, &b0);
+    cudaError_t e1 = repro_conv::conv2d_grad_weight_workspace(g, 3, &b1);
+    cudaError_t e2 = repro_conv::conv2d_grad_input_workspace(g, 3, &b2);
+    cudaError_t bad = repro_conv::conv2d_workspace(g, 4, &b0);
+    cudaError_t run = repro_conv::repro_conv2d_ws(nullptr, nullptr, nullptr, g, 3, nullptr, 0);
+    std::printf("%d %d %d %d %d %d %d %d %d %zu\n", (int)e0, (int)e1, (int)e2, (int)bad, (int)run, g.K(), g.OH(), g.OW(), g.windows(),
+                g.output_size());
+    return (b0 && b1 && b2) ? 0 : 1;
+}
+"""
+
+
+def test_cxx_conv_caller_builds_against_the_shim_and_links_the_library(L, tmp_path):
+    """A C++ program using the reference's ConvShape and workspace queries compiles against
+    include/repro_conv.cuh and links librgb200.so; planning needs no GPU."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    src = tmp_path / "conv_caller.cu"
+    src.write_text(CXX_CONV_CALLER)
+    exe = tmp_path / "conv_caller"
+    libdir = os.path.dirname(build.LIB)
+    subprocess.run([nvcc, "-std=c++17", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src),
+                    "-L", libdir, "-lrgb200", "-Xlinker", "-rpath", "-Xlinker", libdir], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert [int(v) for v in out[:5]] == [0, 0, 0, rg.cudaErrorInvalidValue, rg.cudaErrorInvalidValue]
+    assert [int(v) for v in out[5:]] == [25, 28, 28, 78400, 100 * 6 * 28 * 28]
