@@ -126,3 +126,26 @@ def test_conv2d_layer_autograd_matches_oracle():
     assert np.array_equal(bits(layer.weight.grad), oracle.conv2d_grad_weight(dy, x, shape, 3).reshape(-1).view(np.uint32))
     with pytest.raises(NotImplementedError):
         layers.Conv2d(C, F, 3, dilation=2).cuda()(xin)
+
+
+def test_random_geometries_match_the_oracle():
+    """Forty seeded random layers: kernels up to 5 x 4, strides up to 3 (different per axis), padding up to
+    kernel size, 1 to 40 channels and filters, both input distributions, every S."""
+    rng = np.random.default_rng(20241125)
+    for case in range(40):
+        KH, KW = int(rng.integers(1, 6)), int(rng.integers(1, 5))
+        SY, SX = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        PY, PX = int(rng.integers(0, KH + 1)), int(rng.integers(0, KW + 1))
+        H, W = max(1, KH - 2 * PY) + int(rng.integers(0, 12)), max(1, KW - 2 * PX) + int(rng.integers(0, 12))
+        N, C, F = int(rng.integers(1, 5)), int(rng.choice([1, 2, 3, 4, 5, 8, 16, 17, 40])), int(rng.choice([1, 3, 4, 7, 16, 20, 33]))
+        shape = (N, C, H, W, F, KH, KW, SY, SX, PY, PX)
+        S = int(rng.integers(1, 4))
+        x, w, dy = fx.conv_inputs(shape, "wide" if case % 3 == 0 else "normal", seed=1000 + case)
+        g = rc.ConvShape(*shape)
+        assert g.OH() >= 1 and g.OW() >= 1
+        dx_, dw_, ddy = dev(x), dev(w), dev(dy)
+        assert np.array_equal(bits(rc.conv2d(dx_, dw_, g, S)), oracle.conv2d(x, w, shape, S).reshape(-1).view(np.uint32)), (shape, S, "forward")
+        assert np.array_equal(bits(rc.conv2d_grad_weight(ddy, dx_, g, S)),
+                              oracle.conv2d_grad_weight(dy, x, shape, S).reshape(-1).view(np.uint32)), (shape, S, "dW")
+        assert np.array_equal(bits(rc.conv2d_grad_input(ddy, dw_, g, S)),
+                              oracle.conv2d_grad_input(dy, w, shape, S).reshape(-1).view(np.uint32)), (shape, S, "dX")
