@@ -1,6 +1,8 @@
 """Benchmark of the integer-exact FP32 GEMM path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode rows|ksplit]
+    python bench.py --workload c1|c2|c4|c5                            (the other GEMM configurations, one GPU)
+    python bench.py --workload conv-lenet1|conv-lenet2|conv-mid       (one convolution layer, one GPU)
 
 One step = one full pass of the hot path (split pre-pass, int8 MMA mainloop, fused rounding
 epilogue) over one 4096 x 4096 x 4096, S = 3 GEMM with the wide-dynamic-range synthetic inputs.
