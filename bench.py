@@ -1,21 +1,31 @@
 """Benchmark of the integer-exact FP32 GEMM path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode rows|ksplit]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--no-ksplit] [--no-c4] [--no-cpu-baseline] [--int8-library-yardstick]
     python bench.py --workload c1|c2|c4|c5                            (the other GEMM configurations, one GPU)
-    python bench.py --workload conv-lenet1|conv-lenet2|conv-mid       (one convolution layer, one GPU)
+    python bench.py --workload conv-lenet1|conv-lenet2|conv-mid|conv-small|conv-5x5   (one convolution layer, one GPU)
 
 One step = one full pass of the hot path (split pre-pass, int8 MMA mainloop, fused rounding
 epilogue) over one 4096 x 4096 x 4096, S = 3 GEMM with the wide-dynamic-range synthetic inputs.
-With N > 1 GPUs (torchrun, one rank per GPU) the default mode shards rows of A: every rank owns a
+With N > 1 GPUs (torchrun, one rank per GPU) the headline line shards rows of A: every rank owns a
 4096-row block of a (4096 N) x 4096 x 4096 product and the whole B; no collective is on the data
-path (weak scaling).  --mode ksplit instead gives every rank a 4096-wide K range of a
-4096 x 4096 x (4096 N) product and reduces the exact INT64 partial sums with NCCL; --mode
-ksplit-fused lets the MMA epilogue store the partial sums straight into the owning rank's memory.
+path (weak scaling).  The same run then times, as sub-records of the line,
+  * "ksplit" / "ksplit_fused": every rank holds a 4096-wide K range of a 4096 x 4096 x (4096 N) product;
+    the exact INT64 partial sums are reduced with NCCL, or stored by the MMA epilogue straight into the
+    owning rank's memory;
+  * "c4": the 16384^3 product of configuration 4 sharded over the N ranks by rows of A and by K ranges
+    (strong scaling: the total work is fixed).
+Every timed variant's output is hashed (FNV-1a-64) and compared with the value the reference's CPU
+implementation produced for the same seeded inputs; a mismatch makes the run exit with status 3, as
+the reference's own benchmark refuses a timing whose hash is wrong
+(repro_gemm_cuda/bench_repro_gemm.cu:62-68,116,149).
 
 Prints one JSON line (rank 0).  `value` is 2 M N K / time summed over ranks with the inputs
-resident in HBM; `e2e` repeats the measurement through the host-buffer call (pinned host memory,
-copies inside the timed region, overlapped with compute block by block).  --impl reference times the reference's CPU implementation
-(oracle/_ref, built from the reference's sources) on a bounded sample of the same workload.
+resident in HBM; `e2e` repeats the measurement through the host-buffer entry point of the C ABI
+(rgb200_gemm_fp32_host: pinned host memory, copies inside the timed region, overlapped with compute
+block by block) and reports beside it what plain copies of the same bytes take (`e2e.pcie`).
+--impl reference times the reference's CPU implementation (oracle/_ref, built from the reference's
+sources) on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -34,9 +44,15 @@ METRIC = "bit-exact FP32 GEMM TFLOP/s (2MNK/t), S=3, 4096^3"
 WORKLOAD = ("C=A.B fp32, M=N=K=4096 per GPU, S=3 int8 slices, wide-dynamic-range inputs "
             "(1% zeros, 0.1% subnormals), seed 3")
 NOMINAL_INT8_TOPS = 4500.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one MMA-kernel launch at this workload, from the
-# ncu capture summarised in profiles/gemm_i8_tcgen05_4096cubed_S3.md (193.0 MB read + 53.3 MB written)
+# dram__bytes_read.sum + dram__bytes_write.sum of one MMA-kernel launch at this workload, from one ncu
+# capture of that launch (193.0 MB read + 53.3 MB written); a constant, not re-measured by a bench run
 MMA_DRAM_TRAFFIC_BYTES = 246.3e6
+GOLDEN = os.path.join(ROOT, "tests", "golden", "gemm_hashes.json")
+
+
+def golden_record(name, slices=SLICES):
+    with open(GOLDEN) as f:
+        return [r for r in json.load(f) if r["name"] == name and r["S"] == slices][0]
 
 
 def measured_peaks():
@@ -103,10 +119,9 @@ def cpu_reference_run(steps, warmup, sample_rows):
     """Times the reference's cpu_gemm (or the restated oracle if that library is absent) on the first
     `sample_rows` rows of A against the whole B.  Returns (TFLOP/s, seconds per step, info)."""
     import oracle
-    from bit_reproducible_training_b200 import fixtures as fx
-    c = fx.config3(SIZE)[0]
-    A = c["A"][:sample_rows * SIZE]
-    B = c["B"]
+    g = oracle.Rng(3)                          # configuration 3's stream: A first, then B
+    A = g.wide_mixed(SIZE * SIZE)[:sample_rows * SIZE]
+    B = g.wide_mixed(SIZE * SIZE)
     use_ref = oracle.ref() is not None
     fn = (lambda: oracle.ref_gemm(A, B, sample_rows, SIZE, SIZE, False, False, SLICES)) if use_ref else \
          (lambda: oracle.gemm(A, B, sample_rows, SIZE, SIZE, False, False, SLICES))
@@ -144,8 +159,16 @@ def auxiliary_workload(args):
     from bit_reproducible_training_b200 import fixtures as fx
     from bit_reproducible_training_b200 import repro_gemm as rg
     torch.cuda.set_device(0)
-    cases = {"c1": fx.config1, "c2": fx.config2, "c4": fx.config4, "c5": fx.config5}[args.workload]()
-    with open(os.path.join(ROOT, "tests", "golden", "gemm_hashes.json")) as f:
+    if args.workload == "c4":       # the large operands are generated on the device (same bits, far quicker)
+        A, B = fx.config4_device("cuda")
+        cases = [dict(name="c4.16384", M=16384, N=16384, K=16384, trans_a=False, trans_b=False, A=A, B=B)]
+    elif args.workload == "c5":
+        Q, Km, V, P = fx.config5_device("cuda")
+        cases = [dict(name="c5.QKt", batch=96, M=1024, N=1024, K=64, trans_a=False, trans_b=True, A=Q, B=Km),
+                 dict(name="c5.PV", batch=96, M=1024, N=64, K=1024, trans_a=False, trans_b=False, A=P, B=V)]
+    else:
+        cases = {"c1": fx.config1, "c2": fx.config2}[args.workload]()
+    with open(GOLDEN) as f:
         golden = {(r["name"], r["S"]): r["out_hash"] for r in json.load(f)}
     flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
     prepared, flops = [], 0.0
@@ -156,45 +179,66 @@ def auxiliary_workload(args):
         rc, plan = rg.make_plan(M, N, K, cfg, batch=batch)
         if rc != 0:
             raise rg.ReproGemmError(rc, "make_plan")
-        prepared.append((c, cfg, batch, torch.from_numpy(c["A"]).cuda(), torch.from_numpy(c["B"]).cuda(),
+        on_dev = lambda x: x if isinstance(x, torch.Tensor) else torch.from_numpy(x).cuda()
+        prepared.append((c, cfg, batch, on_dev(c["A"]), on_dev(c["B"]),
                          torch.empty(batch * M * N, dtype=torch.float32, device="cuda"),
                          torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")))
         flops += 2.0 * batch * M * N * K
 
-    def step():
-        for c, cfg, batch, dA, dB, dC, ws in prepared:
-            M, N, K = c["M"], c["N"], c["K"]
-            if batch == 1:
-                rc = rg.repro_gemm_fp32_ws(dA, dB, dC, M, N, K, cfg, ws)
-            else:
-                rc = rg.repro_gemm_fp32_batched_ws(dA, dB, dC, M, N, K, batch, M * K, K * N, M * N, cfg, ws)
-            if rc != 0:
-                raise rg.ReproGemmError(rc, c["name"])
+    def run(item):
+        c, cfg, batch, dA, dB, dC, ws = item
+        M, N, K = c["M"], c["N"], c["K"]
+        if batch == 1:
+            rc = rg.repro_gemm_fp32_ws(dA, dB, dC, M, N, K, cfg, ws)
+        else:
+            rc = rg.repro_gemm_fp32_batched_ws(dA, dB, dC, M, N, K, batch, M * K, K * N, M * N, cfg, ws)
+        if rc != 0:
+            raise rg.ReproGemmError(rc, c["name"])
 
-    for _ in range(max(args.warmup, 3)):
-        flush.zero_()
-        step()
-    torch.cuda.synchronize()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for a, b in ev:
-        flush.zero_()
-        a.record()
-        step()
-        b.record()
-    torch.cuda.synchronize()
-    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
-    ok = True
-    for c, cfg, batch, dA, dB, dC, ws in prepared:
+    warmup = max(args.warmup, 3)
+    peaks = measured_peaks()
+    per_case, total_ms, ok = [], 0.0, True
+    for item in prepared:                      # every case is timed by itself, L2 flushed before each run
+        c, cfg, batch, dA, dB, dC, ws = item
+        for _ in range(warmup):
+            flush.zero_()
+            run(item)
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in ev:
+            flush.zero_()
+            a.record()
+            run(item)
+            b.record()
+        torch.cuda.synchronize()
+        ms = statistics.mean(a.elapsed_time(b) for a, b in ev)
+        total_ms += ms
         name = c["name"] + (".b%d" % batch if "batch" in c else "")
         want = golden.get((name, SLICES))
-        ok = ok and want is not None and ("%016x" % rg.fnv1a64(dC)) == want
-    print(json.dumps({"metric": "bit-exact FP32 GEMM TFLOP/s (2MNK/t), S=3", "value": flops / (ms * 1e-3) / 1e12,
-                      "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
-                      "ms_per_step": ms, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
-                      "auxiliary": True, "output_matches_golden": ok,
-                      "config": {"workload": args.workload + ": " + ", ".join(
-                          "%s %s%dx%dx%d" % (c["name"], ("%d x " % c["batch"]) if "batch" in c else "", c["M"], c["N"], c["K"])
-                          for c in cases), "l2": "512 MiB buffer written between timed iterations (L2 flush)"}}), flush=True)
+        match = want is not None and ("%016x" % rg.fnv1a64(dC)) == want
+        ok = ok and match
+        M, N, K = c["M"], c["N"], c["K"]
+        # algorithmic bytes of a whole call: (4 + S) per operand element (one FP32 read, S digit bytes) + 4 per output
+        nbytes = batch * ((4.0 + SLICES) * (M * K + N * K) + 4.0 * M * N)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        per_case.append({"name": name, "ms": ms, "tflops": 2.0 * batch * M * N * K / (ms * 1e-3) / 1e12,
+                         "output_matches_golden": match,
+                         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes": nbytes},
+                         "int8_frac_of_nominal_4500": 2.0 * SLICES * SLICES * batch * M * N * K / (ms * 1e-3) / 1e12 / NOMINAL_INT8_TOPS})
+    line = {"metric": "bit-exact FP32 GEMM TFLOP/s (2MNK/t), S=3", "value": flops / (total_ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": total_ms, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+            "auxiliary": True, "output_matches_golden": ok, "cases": per_case,
+            "config": {"workload": args.workload + ": " + ", ".join(
+                "%s %s%dx%dx%d" % (c["name"], ("%d x " % c["batch"]) if "batch" in c else "", c["M"], c["N"], c["K"])
+                for c in cases), "l2": "512 MiB buffer written between timed iterations (L2 flush)",
+                "peaks": peaks["source"]}}
+    worst = min(per_case, key=lambda r: r["roofline"]["frac"])
+    line["roofline"] = dict(worst["roofline"], kernel="whole call of " + worst["name"] + " (pre-pass + MMA + epilogue)")
+    print(json.dumps(line), flush=True)
+    if not ok:
+        sys.exit(3)
 
 
 CONV_BENCH_SHAPES = {
@@ -203,6 +247,9 @@ CONV_BENCH_SHAPES = {
     "conv-lenet2": (100, 6, 14, 14, 16, 5, 5, 1, 1, 0, 0),
     # a mid-size layer (64 -> 64 channels, 3 x 3, 56 x 56 images, batch 32) where the products are large enough for tensor cores
     "conv-mid": (32, 64, 56, 56, 64, 3, 3, 1, 1, 1, 1),
+    # two more layers with enough channels for tensor cores: 16 -> 32 channels 3 x 3 on 32 x 32, 32 -> 64 channels 5 x 5 on 28 x 28
+    "conv-small": (32, 16, 32, 32, 32, 3, 3, 1, 1, 1, 1),
+    "conv-5x5": (64, 32, 28, 28, 64, 5, 5, 1, 1, 2, 2),
 }
 
 
@@ -283,15 +330,223 @@ def conv_workload(args):
                          "sample": "the whole layer once: forward, weight gradient, input gradient (%.2f s)" % cpu_s}}), flush=True)
 
 
+def _max_over_ranks(x, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return float(x)
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _all_ranks_true(flag, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return bool(flag)
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item())
+
+
+def _barrier(world):
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed_loop(step, steps, warmup, flush, world):
+    """`warmup` untimed and `steps` timed calls of step(), the L2 flushed before each, one CUDA-event pair per
+    call on the current stream, barriers on both sides.  Returns (sum of the step times in ms, maximum over
+    ranks; the per-step list of this rank)."""
+    import torch
+    for _ in range(warmup):
+        flush.zero_()
+        step()
+    _barrier(world)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:
+        flush.zero_()
+        a.record()
+        step()
+        b.record()
+    _barrier(world)
+    per_step = [a.elapsed_time(b) for a, b in ev]
+    return _max_over_ranks(sum(per_step), world), per_step
+
+
+def measure_pcie(hA, hB, hC, dA, dB, dC, world, reps=5):
+    """What the link allows for one step's bytes: plain cudaMemcpyAsync copies (one per buffer) of A and B to
+    the device, of C back, and of both directions at once on two streams; all ranks copy at the same time,
+    the slowest rank counts.  Median of `reps`."""
+    import torch
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def once(h2d, d2h):
+        _barrier(world)
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        cur = torch.cuda.current_stream()
+        e0.record(cur)
+        s1.wait_event(e0)
+        s2.wait_event(e0)
+        if h2d:
+            with torch.cuda.stream(s1):
+                dA.copy_(hA, non_blocking=True)
+                dB.copy_(hB, non_blocking=True)
+        if d2h:
+            with torch.cuda.stream(s2):
+                hC.copy_(dC, non_blocking=True)
+        e1.record(s1)
+        e2.record(s2)
+        torch.cuda.synchronize()
+        return max(e0.elapsed_time(e1), e0.elapsed_time(e2))
+
+    out = {}
+    for key, h2d, d2h in (("h2d_ms", True, False), ("d2h_ms", False, True), ("duplex_ms", True, True)):
+        once(h2d, d2h)
+        out[key] = _max_over_ranks(statistics.median(once(h2d, d2h) for _ in range(reps)), world)
+    nin, nout = (hA.numel() + hB.numel()) * 4, hC.numel() * 4
+    out["h2d_gbs"] = nin / (out["h2d_ms"] * 1e-3) / 1e9
+    out["d2h_gbs"] = nout / (out["d2h_ms"] * 1e-3) / 1e9
+    out["ranks_copying_at_once"] = world
+    out["how"] = "plain cudaMemcpyAsync of the step's buffers from/to pinned memory, one copy per buffer; duplex = both directions at once"
+    return out
+
+
+def ksplit_records(args, world, rank, dA, dB, dC, cfg, flush, rows_ms):
+    """The 4096 x 4096 x (4096 N) product with one K range per rank, NCCL form and fused form."""
+    import torch
+    from bit_reproducible_training_b200 import repro_gemm as rg
+    from bit_reproducible_training_b200 import sharded
+    M = N = K = SIZE
+    want = golden_record("c3.4096.kcat%d" % world)["out_hash"] if world in (2, 4, 8) else None
+    out = {}
+    steps = min(args.steps, 20)
+    own = M // world
+    for key, fused in (("ksplit", False), ("ksplit_fused", True)):
+        ks = sharded.KSplitState(M, N, K, world, cfg, dA, dB, fused=fused)
+        dC.fill_(float("nan"))
+        total_ms, _ = timed_loop(lambda: ks.step(dC), steps, 3, flush, world)
+        ms = total_ms / steps
+        ok = None
+        if want is not None:
+            ok = _all_ranks_true(("%016x" % rg.fnv1a64(dC)) == want, world)
+        # bytes this rank sends: its INT64 sums for the other owners' row blocks, then its rounded FP32 rows to the others
+        comm = (world - 1) * own * N * 8 + (world - 1) * own * N * 4 + (M + N) * 4
+        out[key] = {"ms_per_step": ms, "value": 2.0 * M * N * K * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "steps": steps, "efficiency_vs_rows": rows_ms / ms, "matches_golden": ok,
+                    "comm_bytes_per_rank": comm, "launches_per_step": ks.launches_per_step,
+                    "what": ("K ranges; maxima all-reduce, INT64 reduce-scatter by row blocks (NCCL), one rounding per owner, FP32 all-gather"
+                             if not fused else
+                             "K ranges; maxima all-reduce, MMA epilogue stores INT64 tiles into the row owners over NVLink, one rounding per owner, FP32 all-gather")}
+        del ks
+        torch.cuda.empty_cache()
+    return out
+
+
+def c4_records(args, world, rank, flush):
+    """Configuration 4 (16384^3, S = 3) over the ranks: rows of A (no collective) and K ranges (both forms).
+    Every rank checks its own 2048-row blocks of the result against the reference's hashes."""
+    import torch
+    from bit_reproducible_training_b200 import fixtures as fx
+    from bit_reproducible_training_b200 import repro_gemm as rg
+    from bit_reproducible_training_b200 import sharded
+    n = 16384
+    rec = golden_record("c4.16384")
+    blk = rec["row_block_hashes"]["rows"]
+    hashes = rec["row_block_hashes"]["hashes"]
+    cfg = rg.Config(slices=SLICES)
+    own = n // world
+    lo = rank * own
+    steps, warm = 5, 3
+    flops = 2.0 * n * n * n
+
+    def blocks_match(C_rows, first_row):
+        ok = True
+        for r0 in range(0, C_rows.shape[0], blk):
+            ok = ok and ("%016x" % rg.fnv1a64(C_rows[r0:r0 + blk])) == hashes[(first_row + r0) // blk]
+        return _all_ranks_true(ok, world)
+
+    out = {"workload": "C=A.B fp32, M=N=K=16384 in total, S=3, uniform[-1,1) inputs, seed 4", "scaling": "strong"}
+    # rows of A
+    A_rows, B = fx.config4_device("cuda", n, a_rows=(lo, lo + own))
+    rc, plan = rg.make_plan(own, n, n, cfg)
+    if rc != 0:
+        raise rg.ReproGemmError(rc, "make_plan c4 rows")
+    ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device="cuda")
+    C_rows = torch.full((own, n), float("nan"), dtype=torch.float32, device="cuda")
+
+    def rows_step():
+        code = rg.repro_gemm_fp32_ws(A_rows, B, C_rows, own, n, n, cfg, ws)
+        if code != 0:
+            raise rg.ReproGemmError(code, "c4 rows")
+    total_ms, _ = timed_loop(rows_step, steps, warm, flush, world)
+    rows_ms = total_ms / steps
+    out["rows"] = {"ms_per_step": rows_ms, "value": flops / (rows_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": steps,
+                   "matches_golden": blocks_match(C_rows, lo), "comm_bytes_per_rank": 0,
+                   "what": "rank r computes rows [r*16384/N, (r+1)*16384/N) against the whole B; no collective"}
+    del A_rows, B, ws, C_rows
+    torch.cuda.empty_cache()
+    if world == 1 or args.no_ksplit:
+        return out
+    # K ranges
+    A_k, B_k = fx.config4_device_k_range("cuda", n, lo, lo + own)
+    C_full = torch.full((n, n), float("nan"), dtype=torch.float32, device="cuda")
+    for key, fused in (("ksplit", False), ("ksplit_fused", True)):
+        ks = sharded.KSplitState(n, n, own, world, cfg, A_k, B_k, fused=fused)
+        C_full.fill_(float("nan"))
+        total_ms, _ = timed_loop(lambda: ks.step(C_full.view(-1)), steps, warm, flush, world)
+        ms = total_ms / steps
+        out[key] = {"ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": steps,
+                    "matches_golden": blocks_match(C_full[lo:lo + own], lo), "efficiency_vs_rows": rows_ms / ms,
+                    "comm_bytes_per_rank": (world - 1) * own * n * 12 + 2 * n * 4}
+        del ks
+        torch.cuda.empty_cache()
+    return out
+
+
+def int8_library_rate():
+    """Dense INT8 tensor rate of the vendor library on this GPU (torch._int_mm, 8192^3), as a measured yardstick
+    beside the derived peak; None where the call is unavailable."""
+    import torch
+    try:
+        n = 8192
+        a = torch.randint(-127, 127, (n, n), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 127, (n, n), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None or ms < best else best
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--mode", default="rows", choices=["rows", "ksplit", "ksplit-fused"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--check", action="store_true", help="also compare the output hash with the golden value")
+    ap.add_argument("--no-ksplit", action="store_true", help="skip the K-range sub-records of a multi-GPU run")
+    ap.add_argument("--no-c4", action="store_true", help="skip the 16384^3 (configuration 4) sub-record")
+    ap.add_argument("--int8-library-yardstick", action="store_true",
+                    help="also time the vendor library's dense INT8 GEMM (torch._int_mm, 8192^3) after the timed regions and "
+                         "report it beside the derived INT8 peak; off by default so that a plain run launches this "
+                         "repository's kernels only")
     ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"] + sorted(CONV_BENCH_SHAPES),
                     help="c3 (default) is the headline 4096^3 workload; c1, c2, c4, c5 time the remaining GEMM configurations "
                          "and conv-* one convolution layer (forward and both gradients) on one GPU, with a reduced line")
@@ -308,12 +563,10 @@ def main():
             conv_workload(args) if args.workload in CONV_BENCH_SHAPES else auxiliary_workload(args)
         return
 
-    import numpy as np
     import torch
     import torch.distributed as dist
     from bit_reproducible_training_b200 import fixtures as fx
     from bit_reproducible_training_b200 import repro_gemm as rg
-    from bit_reproducible_training_b200 import sharded
 
     args.warmup = max(args.warmup, 3)
     torch.cuda.set_device(local_rank)
@@ -321,13 +574,13 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     M = N = K = SIZE
     S = SLICES
-    # the same synthetic operands on every rank: the values do not influence the time
-    c = fx.config3(SIZE)[0]
-    hA = torch.from_numpy(c["A"]).pin_memory()
-    hB = torch.from_numpy(c["B"]).pin_memory()
+    # the same synthetic operands on every rank (generated on the device; same bits as the numpy recipe)
+    dA, dB = fx.config3_device("cuda", SIZE)
+    golden = golden_record("c3.4096")
+    inputs_ok = ("%016x" % rg.fnv1a64(dB, rg.fnv1a64(dA))) == golden["in_hash"]
+    hA, hB = dA.cpu().pin_memory(), dB.cpu().pin_memory()
     hC = torch.empty(M * N, dtype=torch.float32).pin_memory()
-    dA, dB = hA.cuda(), hB.cuda()
-    dC = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    dC = torch.full((M * N,), float("nan"), dtype=torch.float32, device="cuda")
     cfg = rg.Config(slices=S)
     rc, plan = rg.make_plan(M, N, K, cfg)
     if rc != 0:
@@ -339,27 +592,16 @@ def main():
     for evs in stage_ev:
         for e in evs:
             e.record()          # creates the handles the library records into
-    ks = sharded.KSplitState(M, N, K, world, cfg, dA, dB, fused=args.mode == "ksplit-fused") \
-        if (args.mode != "rows" and world > 1) else None
 
     def step(events=None):
-        if ks is not None:
-            ks.step(dC)
-            return
         rc = rg.repro_gemm_fp32_ws(dA, dB, dC, M, N, K, cfg, ws, stream=stream, stage_events=events)
         if rc != 0:
             raise rg.ReproGemmError(rc, "repro_gemm_fp32_ws")
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     for _ in range(args.warmup):
         flush.zero_()
         step()
-    barrier()
+    _barrier(world)
     if rg.workspace_status(ws) != 0:
         raise RuntimeError("a kernel reported an expired wait (status %d)" % rg.workspace_status(ws))
 
@@ -367,99 +609,101 @@ def main():
     if rank == 0:
         sampler.start()
     t_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
+    _barrier(world)
     for i in range(args.steps):
         flush.zero_()                       # L2 flush between timed iterations, outside the timed brackets
         t_ev[i][0].record()
         step(stage_ev[i])
         t_ev[i][1].record()
-    barrier()
+    _barrier(world)
     clocks = sampler.stop() if rank == 0 else None
     step_ms = [a.elapsed_time(b) for a, b in t_ev]
-    total_ms = sum(step_ms)
-    if world > 1:
-        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
+    ms_per_step = _max_over_ranks(sum(step_ms), world) / args.steps
     flops_step = 2.0 * M * N * K * world
     value = flops_step / (ms_per_step * 1e-3) / 1e12
+    device_ok = _all_ranks_true(("%016x" % rg.fnv1a64(dC)) == golden["out_hash"], world)
 
     # per-stage durations from the four events the library records inside each call
-    stages = None
-    if ks is None:
-        pre = [e[0].elapsed_time(e[1]) for e in stage_ev]
-        mma = [e[1].elapsed_time(e[2]) for e in stage_ev]
-        fin = [e[2].elapsed_time(e[3]) for e in stage_ev]
-        def spread(v):      # median [min, p90], the form the reference's stage benchmark prints
-            v = sorted(v)
-            return {"median": statistics.median(v), "min": v[0], "p90": v[min(len(v) - 1, int(0.9 * len(v)))]}
-        stages = {"prepass_ms": statistics.mean(pre), "mma_ms": statistics.mean(mma), "final_ms": statistics.mean(fin),
-                  "prepass_ms_spread": spread(pre), "mma_ms_spread": spread(mma), "step_ms_spread": spread(step_ms)}
+    pre = [e[0].elapsed_time(e[1]) for e in stage_ev]
+    mma = [e[1].elapsed_time(e[2]) for e in stage_ev]
+    fin = [e[2].elapsed_time(e[3]) for e in stage_ev]
 
-    # ---------------- end to end: host buffers in, host buffer out, copies inside the timed region
-    e2e_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    host_gemm = rg.HostGemm(M, N, K, cfg)        # pinned host buffers in and out, copies overlapped with compute
-    for _ in range(2):
-        host_gemm(hA, hB, hC)
-    barrier()
-    for i in range(args.steps):
-        flush.zero_()
-        e2e_ev[i][0].record()
-        host_gemm(hA, hB, hC)
-        e2e_ev[i][1].record()
-    barrier()
-    e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_ev)
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = flops_step / (e2e_ms / args.steps * 1e-3) / 1e12
+    def spread(v):      # median [min, p90], the form the reference's stage benchmark prints
+        v = sorted(v)
+        return {"median": statistics.median(v), "min": v[0], "p90": v[min(len(v) - 1, int(0.9 * len(v)))]}
+    stages = {"prepass_ms": statistics.mean(pre), "mma_ms": statistics.mean(mma), "final_ms": statistics.mean(fin),
+              "prepass_ms_spread": spread(pre), "mma_ms_spread": spread(mma), "step_ms_spread": spread(step_ms)}
 
-    check = None
-    if args.check and rank == 0:
-        with open(os.path.join(ROOT, "tests", "golden", "gemm_hashes.json")) as f:
-            want = [r for r in json.load(f) if r["name"] == "c3.4096" and r["S"] == S][0]["out_hash"]
-        check = ("%016x" % rg.fnv1a64(hC.numpy())) == want
+    # ---------------- end to end: host buffers in, host buffer out, copies inside the timed region,
+    # through the C ABI's host-buffer entry point
+    host_gemm = rg.HostGemm(M, N, K, cfg)
+    hC.fill_(float("nan"))
+    e2e_total, _ = timed_loop(lambda: host_gemm(hA, hB, hC), args.steps, 2, flush, world)
+    e2e_ms = e2e_total / args.steps
+    e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+    e2e_ok = _all_ranks_true(("%016x" % rg.fnv1a64(hC)) == golden["out_hash"] and host_gemm.status() == 0, world)
+    pcie = measure_pcie(hA, hB, hC, dA, dB, dC, world)
+    e2e_launches = host_gemm.launches
+    host_gemm.close()
 
+    sub = {}
+    if world > 1 and not args.no_ksplit:
+        sub.update(ksplit_records(args, world, rank, dA, dB, dC, cfg, flush, ms_per_step))
+    int8_lib = int8_library_rate() if (rank == 0 and args.int8_library_yardstick) else None
+    del dA, dB, dC, ws, hA, hB, hC
+    torch.cuda.empty_cache()
+    if not args.no_c4:
+        sub["c4"] = c4_records(args, world, rank, flush)
+
+    all_ok = inputs_ok and device_ok and e2e_ok
+    for rec in list(sub.values()):
+        for v in ([rec] + [x for x in rec.values() if isinstance(x, dict)]):
+            if isinstance(v, dict) and v.get("matches_golden") is False:
+                all_ok = False
     if rank == 0:
         peaks = measured_peaks()
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                 "config": {"workload": WORKLOAD,
-                           "sharding": "none" if world == 1 else ("rows of A, no collective" if ks is None else
-                                                                  ("K ranges, NCCL int64 reduce-scatter + fp32 all-gather" if args.mode == "ksplit" else
-                                                                   "K ranges, epilogue peer stores into the row owners + fp32 all-gather")),
+                           "sharding": "none" if world == 1 else "rows of A, no collective",
                            "l2": "512 MiB buffer written between timed iterations (L2 flush)"},
                 "clocks": clocks,
+                "inputs_match_golden": inputs_ok, "output_matches_golden": device_ok,
                 "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 4,
-                        "d2h_bytes_per_step": M * N * 4},
-                "gpu_launches": (4 if ks is None else ks.launches_per_step) * args.steps,
-                "e2e_gpu_launches": (4 * len(host_gemm.blocks) + host_gemm.blocks_with_k_ranges) * args.steps}
-        if stages:
-            mma_ops = 2.0 * S * S * M * N * K
-            achieved = mma_ops / (stages["mma_ms"] * 1e-3) / 1e12
-            peak = 2.0 * peaks["bf16_tflops"]
-            line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                                "frac": achieved / peak, "traffic": MMA_DRAM_TRAFFIC_BYTES,
-                                "kernel": "gemm_i8_tcgen05_kernel<3,64>",
-                                "note": "int8 ops/s of the slice-pair MMAs (2*S^2*M*N*K per launch); peak = 2 x the %s "
-                                        "dense bf16 cuBLAS rate (kind::i8 issues at twice the bf16 rate)" % peaks["source"],
-                                "frac_of_nominal_int8_4500": achieved / NOMINAL_INT8_TOPS}
-            line["stages"] = stages
-            pre_bytes = (4.0 + S) * (M * K + N * K) + 4.0 * (M + N)
-            line["prepass_roofline"] = {"bound": "hbm", "achieved": pre_bytes / (stages["prepass_ms"] * 1e-3) / 1e9,
-                                        "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                        "frac": pre_bytes / (stages["prepass_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-        if check is not None:
-            line["output_matches_golden"] = check
+                        "d2h_bytes_per_step": M * N * 4, "ms_per_step": e2e_ms, "output_matches_golden": e2e_ok,
+                        "through": "rgb200_gemm_fp32_host (C ABI), pinned host buffers", "pcie": pcie,
+                        "frac": pcie["duplex_ms"] / e2e_ms,
+                        "frac_note": "time of plain copies of the same bytes (both directions at once, all ranks at once) / e2e step"},
+                "gpu_launches": 4 * args.steps,
+                "e2e_gpu_launches": e2e_launches * args.steps}
+        mma_ops = 2.0 * S * S * M * N * K
+        achieved = mma_ops / (stages["mma_ms"] * 1e-3) / 1e12
+        peak = 2.0 * peaks["bf16_tflops"]
+        line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                            "frac": achieved / peak, "traffic": MMA_DRAM_TRAFFIC_BYTES,
+                            "traffic_source": "one ncu capture of this kernel at this workload (dram__bytes_read.sum + "
+                                              "dram__bytes_write.sum); a recorded constant, not re-measured by this run",
+                            "kernel": "gemm_i8_tcgen05_kernel<3,64>",
+                            "note": "int8 ops/s of the slice-pair MMAs (2*S^2*M*N*K per launch); peak = 2 x the %s "
+                                    "dense bf16 cuBLAS rate (kind::i8 issues at twice the bf16 rate)" % peaks["source"],
+                            "frac_of_nominal_int8_4500": achieved / NOMINAL_INT8_TOPS,
+                            "int8_library_tops_measured_here": int8_lib,
+                            "frac_of_int8_library": (achieved / int8_lib) if int8_lib else None}
+        line["stages"] = stages
+        pre_bytes = (4.0 + S) * (M * K + N * K) + 4.0 * (M + N)
+        line["prepass_roofline"] = {"bound": "hbm", "achieved": pre_bytes / (stages["prepass_ms"] * 1e-3) / 1e9,
+                                    "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                    "frac": pre_bytes / (stages["prepass_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        line.update(sub)
         if world == 1 and not args.no_cpu_baseline:
             _, _, info = cpu_reference_run(2, 1, 1024)
             line["cpu_baseline"] = info
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if not all_ok:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -49,6 +49,12 @@ def lib():
     L.rgb200_gemm_fp32_batched_ws.argtypes = [fp, fp, fp, i, i, i, i, ll, ll, ll, cfgp, vp, C.c_size_t, vp,
                                               C.POINTER(vp)]
     L.rgb200_gemm_fp32_static.argtypes = [fp, fp, fp, i, i, i, cfgp, vp]
+    L.rgb200_static_status.argtypes = [C.POINTER(C.c_int)]
+    L.rgb200_host_gemm_create.argtypes = [i, i, i, cfgp, i, C.POINTER(vp)]
+    L.rgb200_gemm_fp32_host.argtypes = [vp, fp, fp, fp, vp]
+    L.rgb200_host_gemm_info.argtypes = [vp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
+    L.rgb200_host_gemm_status.argtypes = [vp, C.POINTER(C.c_int)]
+    L.rgb200_host_gemm_destroy.argtypes = [vp]
     L.rgb200_selftest_bounded_wait.argtypes = [ll, C.POINTER(C.c_int), C.POINTER(ll), C.POINTER(C.c_int)]
     L.rgb200_absmax.argtypes = [fp, i, i, i, fp, vp]
     L.rgb200_gemm_partial_ws.argtypes = [fp, fp, fp, fp, vp, i, i, i, ll, cfgp, vp, C.c_size_t, vp]

@@ -9,6 +9,8 @@
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
+#include <new>
+#include <vector>
 
 #include "../../include/rgb200.h"
 #include "rgb200_math.cuh"
@@ -42,9 +44,9 @@ struct Layout {
     int Kp, k_blocks, min_split, split;
     bool partial_out;          // the caller receives INT64 sums instead of C
     bool use_partial_ws;       // K ranges are reduced through the workspace
-    size_t qa, qb, ea, eb, scratch, part;   // byte offsets into the workspace
-    size_t max_a, max_b, status;            // inside the zero-initialised scratch block
-    size_t scratch_bytes, total;
+    size_t qa, qb, ea, eb, part;            // byte offsets into the workspace
+    size_t max_a, max_b, status;            // inside the two zero-initialised blocks
+    size_t zero_b_bytes, zero_a_bytes, total;
     int algo;
 };
 
@@ -116,18 +118,19 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
 
     const size_t qa_bytes = (size_t)batch * S * M * L.Kp, qb_bytes = (size_t)batch * S * N * L.Kp;
     const size_t part_bytes = L.use_partial_ws ? (size_t)L.split * batch * M * N * sizeof(long long) : 0;
-    // zero-initialised scratch block first: status word (fixed place: the first word of the workspace),
-    // then the integer column maxima of the k-strided pre-pass
+    // Everything that belongs to op(B) comes first and its offsets do not depend on M, so consecutive calls on
+    // row blocks of one product can share B's digit planes (see RunArgs::reuse_b).  Two zero-initialised
+    // blocks: [status word | integer column maxima of B] at the start, the maxima of A in front of A's planes.
     L.status = 0;
-    L.max_a = ALIGN;
-    L.max_b = L.max_a + align_up((size_t)batch * M * sizeof(uint32_t));
-    L.scratch = 0;
-    L.scratch_bytes = L.max_b + align_up((size_t)batch * N * sizeof(uint32_t));
-    L.qa = L.scratch_bytes;
-    L.qb = L.qa + align_up(qa_bytes);
-    L.ea = L.qb + align_up(qb_bytes);
-    L.eb = L.ea + align_up((size_t)batch * M * sizeof(int));
-    L.part = L.eb + align_up((size_t)batch * N * sizeof(int));
+    L.max_b = ALIGN;
+    L.zero_b_bytes = L.max_b + align_up((size_t)batch * N * sizeof(uint32_t));
+    L.qb = L.zero_b_bytes;
+    L.eb = L.qb + align_up(qb_bytes);
+    L.max_a = L.eb + align_up((size_t)batch * N * sizeof(int));
+    L.zero_a_bytes = align_up((size_t)batch * M * sizeof(uint32_t));
+    L.qa = L.max_a + L.zero_a_bytes;
+    L.ea = L.qa + align_up(qa_bytes);
+    L.part = L.ea + align_up((size_t)batch * M * sizeof(int));
     L.total = L.part + align_up(part_bytes);
     return cudaSuccess;
 }
@@ -324,6 +327,9 @@ struct RunArgs {
     int scatter_world = 0, scatter_rank = 0;
     const PrepassHook* hook = nullptr;
     int c_image_rows = 0;                  // > 0: image-major C (see GemmParams::c_image_rows); needs split == 1
+    // B's digit planes and exponents already sit in the workspace from the previous call on it with the same
+    // N, K, S and transposition (row blocks of one product): skip B's pre-pass.
+    bool reuse_b = false;
 };
 
 template <int S>
@@ -344,10 +350,16 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     // and clears the status word; no column maxima are needed, hence no memset either.
     const bool both_kmajor = !a.trans_a && a.trans_b;
     if (a.hook) {
-        e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);
-        if (e != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(a.ws, 0, L.zero_b_bytes, a.st)) != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(a.ws + L.max_a, 0, L.zero_a_bytes, a.st)) != cudaSuccess) return e;
         record(0);
         if ((e = a.hook->launch(a.hook->ctx, L, max_a, max_b, qa, qb, ea, eb, a.st)) != cudaSuccess) return e;
+        record(1);
+    } else if (a.reuse_b) {
+        // B's planes and exponents are those of the previous call on this workspace (same N, K, S): only A is split
+        if (a.trans_a && (e = cudaMemsetAsync(a.ws + L.max_a, 0, L.zero_a_bytes, a.st)) != cudaSuccess) return e;
+        record(0);
+        launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, a.st);
         record(1);
     } else if (both_kmajor) {
         record(0);
@@ -356,8 +368,8 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         launch_kmajor<S>(opa, opb, L.K, L.Kp, L.batch, status, a.st);
         record(1);
     } else {
-        e = cudaMemsetAsync(a.ws + L.scratch, 0, L.scratch_bytes, a.st);   // column maxima + status word
-        if (e != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(a.ws, 0, L.zero_b_bytes, a.st)) != cudaSuccess) return e;   // status word + column maxima of B
+        if (a.trans_a && (e = cudaMemsetAsync(a.ws + L.max_a, 0, L.zero_a_bytes, a.st)) != cudaSuccess) return e;
         record(0);
         // The two operands are independent until the MMA kernel.  For large operands A's split runs on a side
         // stream next to B's (fork and join by events, so the caller's stream still orders everything; this
@@ -459,6 +471,46 @@ cudaError_t gemm_ws(const float* A, const float* B, float* C, int M, int N, int 
     return dispatch(L, a, *dev);
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Host-buffer pipeline.  The reference's tools surround every product with whole-matrix copies
+// (repro_gemm_cuda/hash_repro_gemm.cu:117-118,139); here B travels first, A follows in row blocks, and
+// for each block the split, the MMA kernel and the copy of the finished rows of C back to the host run
+// while the next block of A is still on the link (three streams: copy-in, compute, copy-out).  Row
+// blocks are independent products (scales and sums never cross rows), so the bits equal one call's.
+// B is split once, by the first block's call; later blocks reuse its planes (RunArgs::reuse_b).
+// ------------------------------------------------------------------------------------------
+struct HostBlock { int lo, rows; };
+}  // namespace
+}  // namespace rgb200
+
+struct rgb200_host_gemm {
+    int M, N, K, device;
+    rgb200_config cfg;
+    std::vector<rgb200::HostBlock> blocks;
+    std::vector<rgb200::Layout> layouts;      // one per block
+    float *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    char* ws = nullptr;
+    size_t ws_bytes = 0;
+    cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_b = nullptr, ev_in_done = nullptr, ev_run_done = nullptr, ev_out_done = nullptr;
+    std::vector<cudaEvent_t> ev_a, ev_c;
+    int launches = 0;
+};
+
+namespace rgb200 {
+namespace {
+
+void host_gemm_free(rgb200_host_gemm* h) {
+    if (!h) return;
+    cudaFree(h->dA); cudaFree(h->dB); cudaFree(h->dC); cudaFree(h->ws);
+    for (cudaStream_t st : {h->s_in, h->s_run, h->s_out}) if (st) cudaStreamDestroy(st);
+    for (cudaEvent_t ev : {h->ev_fork, h->ev_b, h->ev_in_done, h->ev_run_done, h->ev_out_done}) if (ev) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : h->ev_a) if (ev) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : h->ev_c) if (ev) cudaEventDestroy(ev);
+    (void)cudaGetLastError();
+    delete h;
+}
 
 // ------------------------------------------------------------------------------------------
 // Convolutions (reference: repro_conv_cuda/repro_conv.cu:157-238).  Each call is one (batched)
@@ -622,6 +674,9 @@ using namespace rgb200;
 // device object: the address a kernel can use comes from cudaGetSymbolAddress, looked up once per
 // device with that device current (static_workspace_address below).
 static __device__ __align__(256) unsigned char rgb200_static_scratch[RGB200_STATIC_WORKSPACE_BYTES];
+// Scratch of the bounded-wait self-test (status word and three result words); separate from the array above so
+// that the self-test never touches a rgb200_gemm_fp32_static call in flight.
+static __device__ __align__(256) unsigned char rgb200_probe_scratch[256];
 
 namespace {
 void* g_static_ptr[MAX_DEVICES];
@@ -656,9 +711,19 @@ int rgb200_gemm_fp32_static(const float* A, const float* B, float* C, int M, int
     cudaError_t e = plan_layout(M, N, K, K, 1, *cfg, false, L);
     if (e != cudaSuccess) return e;
     if (L.total > (size_t)RGB200_STATIC_WORKSPACE_BYTES) return cudaErrorMemoryAllocation;   // does not fit the fixed array
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;       // "not supported" before any symbol lookup
     void* ws = nullptr;
     if ((e = static_workspace_address(&ws)) != cudaSuccess) return e;
     return gemm_ws(A, B, C, M, N, K, 1, 0, 0, 0, cfg, ws, RGB200_STATIC_WORKSPACE_BYTES, stream, nullptr);
+}
+
+int rgb200_static_status(int* status) {
+    if (!status) return cudaErrorInvalidValue;
+    void* ws = nullptr;
+    cudaError_t e = static_workspace_address(&ws);
+    if (e != cudaSuccess) return e;
+    return cudaMemcpy(status, ws, sizeof(int), cudaMemcpyDeviceToHost);    // the status word leads the array
 }
 
 void rgb200_default_config(rgb200_config* cfg) {
@@ -750,6 +815,142 @@ int rgb200_gemm_fp32_batched_ws(const float* A, const float* B, float* C, int M,
                                 long long stride_a, long long stride_b, long long stride_c, const rgb200_config* cfg,
                                 void* workspace, size_t workspace_bytes, void* stream, void* const* events4) {
     return gemm_ws(A, B, C, M, N, K, batch, stride_a, stride_b, stride_c, cfg, workspace, workspace_bytes, stream, events4);
+}
+
+int rgb200_host_gemm_create(int M, int N, int K, const rgb200_config* cfg, int block_rows, rgb200_host_gemm** handle) {
+    if (!handle || !cfg) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (block_rows <= 0) block_rows = 512;
+    rgb200_host_gemm* h = new (std::nothrow) rgb200_host_gemm();
+    if (!h) return cudaErrorMemoryAllocation;
+    h->M = M; h->N = N; h->K = K; h->cfg = *cfg;
+    cudaError_t e = cudaGetDevice(&h->device);
+    // Row blocks: block_rows each; the last full block is halved repeatedly (down to 128 rows) so that little
+    // compute and little of C remain after the last byte of A has arrived.
+    if (e == cudaSuccess) {
+        Layout probe;
+        e = plan_layout(M, N, K, K, 1, *cfg, false, probe);
+    }
+    const DeviceInfo* dev = nullptr;
+    if (e == cudaSuccess) e = check_device(cfg->algo == RGB200_ALGO_AUTO ? RGB200_ALGO_TENSORCORE : cfg->algo, &dev);
+    if (e != cudaSuccess) { host_gemm_free(h); return e; }
+    int lo = 0;
+    while (lo < M) {
+        int rows = M - lo < block_rows ? M - lo : block_rows;
+        if (M - lo <= block_rows) {                       // the tail: 1/2, 1/4, ... of what is left
+            while (rows > 128 && rows > (M - lo + 1) / 2) rows = (rows + 1) / 2;
+            if (M - lo - rows < 64) rows = M - lo;
+        }
+        h->blocks.push_back({lo, rows});
+        lo += rows;
+    }
+    for (const HostBlock& b : h->blocks) {
+        Layout L;
+        if ((e = plan_layout(b.rows, N, K, K, 1, *cfg, false, L)) != cudaSuccess) { host_gemm_free(h); return e; }
+        h->layouts.push_back(L);
+        h->ws_bytes = L.total > h->ws_bytes ? L.total : h->ws_bytes;
+        // launches per block: A's split (two kernels when A is stored k-strided), the MMA kernel, the K-range reduction
+        h->launches += (cfg->trans_a ? 2 : 1) + 1 + (L.use_partial_ws ? 1 : 0);
+    }
+    // B's split, once per product: two kernels when B is stored k-strided, one when k-contiguous, and none
+    // extra when A is k-contiguous too (the first block's launch then splits both operands)
+    h->launches += cfg->trans_b ? (cfg->trans_a ? 1 : 0) : 2;
+    const size_t na = (size_t)M * K, nb = (size_t)K * N, nc = (size_t)M * N;
+    if ((e = cudaMalloc(&h->dA, na * sizeof(float))) != cudaSuccess || (e = cudaMalloc(&h->dB, nb * sizeof(float))) != cudaSuccess ||
+        (e = cudaMalloc(&h->dC, nc * sizeof(float))) != cudaSuccess || (e = cudaMalloc(&h->ws, h->ws_bytes)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&h->s_run, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking)) != cudaSuccess) { host_gemm_free(h); return e; }
+    for (cudaEvent_t* ev : {&h->ev_fork, &h->ev_b, &h->ev_in_done, &h->ev_run_done, &h->ev_out_done})
+        if ((e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming)) != cudaSuccess) { host_gemm_free(h); return e; }
+    h->ev_a.assign(h->blocks.size(), nullptr);
+    h->ev_c.assign(h->blocks.size(), nullptr);
+    for (size_t i = 0; i < h->blocks.size(); ++i)
+        if ((e = cudaEventCreateWithFlags(&h->ev_a[i], cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&h->ev_c[i], cudaEventDisableTiming)) != cudaSuccess) { host_gemm_free(h); return e; }
+    *handle = h;
+    return cudaSuccess;
+}
+
+int rgb200_host_gemm_destroy(rgb200_host_gemm* handle) {
+    if (!handle) return cudaErrorInvalidValue;
+    cudaError_t e = cudaSetDevice(handle->device);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    host_gemm_free(handle);
+    return e;
+}
+
+int rgb200_host_gemm_info(const rgb200_host_gemm* handle, int* blocks, int* launches, size_t* device_bytes) {
+    if (!handle) return cudaErrorInvalidValue;
+    if (blocks) *blocks = (int)handle->blocks.size();
+    if (launches) *launches = handle->launches;
+    if (device_bytes)
+        *device_bytes = ((size_t)handle->M * handle->K + (size_t)handle->K * handle->N + (size_t)handle->M * handle->N) * sizeof(float) +
+                        handle->ws_bytes;
+    return cudaSuccess;
+}
+
+int rgb200_gemm_fp32_host(rgb200_host_gemm* h, const float* A_host, const float* B_host, float* C_host, void* stream) {
+    if (!h || !A_host || !B_host || !C_host) return cudaErrorInvalidValue;
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) return e;
+    if (cur != h->device) return cudaErrorInvalidDevice;
+    const DeviceInfo* dev = nullptr;
+    if ((e = check_device(h->cfg.algo == RGB200_ALGO_AUTO ? RGB200_ALGO_TENSORCORE : h->cfg.algo, &dev)) != cudaSuccess) return e;
+    cudaStream_t user = static_cast<cudaStream_t>(stream);
+    const int M = h->M, N = h->N, K = h->K;
+    const bool ta = h->cfg.trans_a != 0;
+#define RGB_CK(call) do { if ((e = (call)) != cudaSuccess) return e; } while (0)
+    // fork: the three pipeline streams start after whatever the caller has enqueued on `stream`
+    RGB_CK(cudaEventRecord(h->ev_fork, user));
+    RGB_CK(cudaStreamWaitEvent(h->s_in, h->ev_fork, 0));
+    RGB_CK(cudaStreamWaitEvent(h->s_run, h->ev_fork, 0));
+    RGB_CK(cudaStreamWaitEvent(h->s_out, h->ev_fork, 0));
+    // copy-in: B, then A block by block.  With trans_a the stored matrix is K x M and a row block of op(A) is a
+    // band of columns: a pitched copy packs it into a dense K x rows block at element offset lo * K.
+    RGB_CK(cudaMemcpyAsync(h->dB, B_host, (size_t)K * N * sizeof(float), cudaMemcpyHostToDevice, h->s_in));
+    RGB_CK(cudaEventRecord(h->ev_b, h->s_in));
+    for (size_t i = 0; i < h->blocks.size(); ++i) {
+        const HostBlock& b = h->blocks[i];
+        float* dst = h->dA + (size_t)b.lo * K;
+        if (!ta) RGB_CK(cudaMemcpyAsync(dst, A_host + (size_t)b.lo * K, (size_t)b.rows * K * sizeof(float), cudaMemcpyHostToDevice, h->s_in));
+        else RGB_CK(cudaMemcpy2DAsync(dst, (size_t)b.rows * sizeof(float), A_host + b.lo, (size_t)M * sizeof(float),
+                                      (size_t)b.rows * sizeof(float), (size_t)K, cudaMemcpyHostToDevice, h->s_in));
+        RGB_CK(cudaEventRecord(h->ev_a[i], h->s_in));
+    }
+    RGB_CK(cudaEventRecord(h->ev_in_done, h->s_in));
+    // compute
+    RGB_CK(cudaStreamWaitEvent(h->s_run, h->ev_b, 0));
+    for (size_t i = 0; i < h->blocks.size(); ++i) {
+        const HostBlock& b = h->blocks[i];
+        RGB_CK(cudaStreamWaitEvent(h->s_run, h->ev_a[i], 0));
+        RunArgs a{h->dA + (size_t)b.lo * K, h->dB, h->dC + (size_t)b.lo * N, nullptr, nullptr, nullptr, 0, 0, 0, ta,
+                  h->cfg.trans_b != 0, h->ws, h->s_run, nullptr};
+        a.reuse_b = i > 0;
+        RGB_CK(dispatch(h->layouts[i], a, *dev));
+        RGB_CK(cudaEventRecord(h->ev_c[i], h->s_run));
+    }
+    RGB_CK(cudaEventRecord(h->ev_run_done, h->s_run));
+    // copy-out
+    for (size_t i = 0; i < h->blocks.size(); ++i) {
+        const HostBlock& b = h->blocks[i];
+        RGB_CK(cudaStreamWaitEvent(h->s_out, h->ev_c[i], 0));
+        RGB_CK(cudaMemcpyAsync(C_host + (size_t)b.lo * N, h->dC + (size_t)b.lo * N, (size_t)b.rows * N * sizeof(float),
+                               cudaMemcpyDeviceToHost, h->s_out));
+    }
+    RGB_CK(cudaEventRecord(h->ev_out_done, h->s_out));
+    // join: the caller's stream continues after the last copy into C_host
+    RGB_CK(cudaStreamWaitEvent(user, h->ev_in_done, 0));
+    RGB_CK(cudaStreamWaitEvent(user, h->ev_run_done, 0));
+    RGB_CK(cudaStreamWaitEvent(user, h->ev_out_done, 0));
+#undef RGB_CK
+    return cudaSuccess;
+}
+
+int rgb200_host_gemm_status(const rgb200_host_gemm* handle, int* status) {
+    if (!handle || !status) return cudaErrorInvalidValue;
+    return cudaMemcpy(status, handle->ws, sizeof(int), cudaMemcpyDeviceToHost);
 }
 
 int rgb200_workspace_status(const void* workspace, int* status) {
@@ -878,7 +1079,7 @@ int rgb200_selftest_bounded_wait(long long limit_clocks, int* status, long long*
     cudaError_t e = check_device(RGB200_ALGO_TENSORCORE, &dev);
     if (e != cudaSuccess) return e;
     void* base = nullptr;
-    if ((e = static_workspace_address(&base)) != cudaSuccess) return e;     // scratch from the fixed array: no allocation
+    if ((e = cudaGetSymbolAddress(&base, rgb200_probe_scratch)) != cudaSuccess) return e;   // no allocation
     int* d_status = static_cast<int*>(base);
     long long* d_out = reinterpret_cast<long long*>(static_cast<char*>(base) + 64);
     if ((e = cudaMemset(base, 0, 256)) != cudaSuccess) return e;

@@ -29,9 +29,7 @@
 #include <type_traits>
 #include "rgb200_math.cuh"
 
-// Build-time options.  RGB200_TILE_GROUP_M: row tiles per schedule group.  RGB200_TIMING_STAMPS (off by
-// default): CTA 0 writes clock64 stamps of its first five tiles (MMA start, MMA issued, epilogue sees the
-// accumulators, TMEM released) into the unused part of the workspace's status block, words 1..30.
+// Build-time option.  RGB200_TILE_GROUP_M: row tiles per schedule group.
 #ifndef RGB200_TILE_GROUP_M
 #define RGB200_TILE_GROUP_M 8
 #endif
@@ -359,9 +357,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const TileCoord tc = tile_coord(P, tile);
                 if (!(ok = mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
                 tc_fence_after();
-#ifdef RGB200_TIMING_STAMPS
-                if (blockIdx.x == 0 && tile_it < 5) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 0] = clock64();
-#endif
                 for (int kb = tc.kb_begin; kb < tc.kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -393,9 +388,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     umma_commit(empty_bar(s));          // frees the stage once these MMAs have read it
                 }
                 if (ok) umma_commit(tmem_full_bar);     // accumulators complete
-#ifdef RGB200_TIMING_STAMPS
-                if (blockIdx.x == 0 && tile_it < 5) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 1] = clock64();
-#endif
             }
         }
     } else {
@@ -428,9 +420,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
-#ifdef RGB200_TIMING_STAMPS
-            if (blockIdx.x == 0 && tile_it < 5 && threadIdx.x == 64) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 2] = clock64();
-#endif
             // phase 1: accumulators -> exact INT64 sums in registers, then release TMEM
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * CPT;
             TAcc T[CPT];
@@ -451,9 +440,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             }
             tc_fence_before();
             mbar_arrive(tmem_empty_bar);
-#ifdef RGB200_TIMING_STAMPS
-            if (blockIdx.x == 0 && tile_it < 5 && threadIdx.x == 64) reinterpret_cast<long long*>(P.status)[1 + tile_it * 6 + 3] = clock64();
-#endif
             // phase 2: one rounding per output (or the raw sums), overlapped with the next tile's MMAs
             if (!P.scatter_rows && (!row_ok || col0 >= P.N)) continue;
             if (P.partial) {

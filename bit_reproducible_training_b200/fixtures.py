@@ -304,3 +304,144 @@ def conv_inputs(shape, dist="normal", seed=2024):
     if dist == "wide":
         return tuple(g.wide_mixed(n) for n in sizes)
     return g.normal(sizes[0]), g.normal(sizes[1], 0.1), g.normal(sizes[2], 1e-3)
+
+
+# ------------------------------------------------------------------------------------------------
+# The same streams produced with torch tensor arithmetic on any device (the 16384^2 operands of
+# configuration 4 take minutes with the numpy generator and milliseconds on a GPU).  Every step is an
+# exact integer or float64 operation followed by one IEEE rounding to float32, so the bits equal the
+# numpy generator's; tests compare the two element for element and against the committed input hashes.
+# ------------------------------------------------------------------------------------------------
+class DeviceRng:
+    """SplitMix64 stream on a torch device; methods consume draws in the same order as ``Rng``."""
+
+    _CHUNK = 1 << 24
+
+    def __init__(self, seed, device):
+        import torch
+        self.t = torch
+        self.state = int(seed) & 0xFFFFFFFFFFFFFFFF
+        self.device = torch.device(device)
+
+    @staticmethod
+    def _i64(x):
+        x &= 0xFFFFFFFFFFFFFFFF
+        return x - (1 << 64) if x >= (1 << 63) else x
+
+    def skip(self, n):
+        """Advances the stream by n draws without producing them (the generator is a counter)."""
+        self.state = (self.state + n * int(_GAMMA)) & 0xFFFFFFFFFFFFFFFF
+
+    def _lsr(self, z, k):
+        return (z >> k) & ((1 << (64 - k)) - 1)          # logical shift of a 64-bit pattern held as int64
+
+    def next(self, n):
+        """The next n raw outputs as int64 bit patterns (two's-complement wrap = arithmetic mod 2^64)."""
+        t = self.t
+        idx = t.arange(1, n + 1, dtype=t.int64, device=self.device)
+        z = idx * self._i64(int(_GAMMA)) + self._i64(self.state)
+        self.skip(n)
+        z = (z ^ self._lsr(z, 30)) * self._i64(int(_M1))
+        z = (z ^ self._lsr(z, 27)) * self._i64(int(_M2))
+        return z ^ self._lsr(z, 31)
+
+    def _umod(self, z, m):
+        """z mod m for the unsigned 64-bit value behind an int64 pattern (m < 2^31)."""
+        hi, lo = self._lsr(z, 32), z & 0xFFFFFFFF
+        return ((hi % m) * ((1 << 32) % m) + lo % m) % m
+
+    def _u01_of(self, z):
+        return self._lsr(z, 40).to(self.t.float64) * (1.0 / 16777216.0)
+
+    def _pow2(self, e):
+        """2^e as float64 for an int64 tensor of exponents in the normal range, built from its bit pattern."""
+        return ((e + 1023) << 52).view(self.t.float64)
+
+    def _chunks(self, n, per_elem, one):
+        out = self.t.empty(n, dtype=self.t.float32, device=self.device)
+        step = max(1, self._CHUNK // per_elem)
+        for lo in range(0, n, step):
+            hi = min(n, lo + step)
+            out[lo:hi] = one(hi - lo)
+        return out
+
+    def uniform_pm1(self, n):
+        return self._chunks(n, 1, lambda m: (2.0 * self._u01_of(self.next(m)) - 1.0).to(self.t.float32))
+
+    def normal(self, n, scale=1.0):
+        def one(m):
+            u = self._u01_of(self.next(12 * m)).view(m, 12)
+            acc = self.t.zeros(m, dtype=self.t.float64, device=self.device)
+            for i in range(12):
+                acc = acc + u[:, i]
+            return (scale * (acc - 6.0)).to(self.t.float32)
+        return self._chunks(n, 12, one)
+
+    def wide_mixed(self, n, elo=-20, ehi=20):
+        t = self.t
+
+        def one(m):
+            z = self.next(4 * m).view(m, 4)
+            r = self._umod(z[:, 0], 1000)
+            mant = 1.0 + self._u01_of(z[:, 1])
+            e = t.where(r == 10, -149 + self._umod(z[:, 2], 23), elo + self._umod(z[:, 2], ehi - elo + 1))
+            v = mant * self._pow2(e)
+            v = t.where((z[:, 3] & 1) != 0, -v, v)
+            return t.where(r < 10, t.zeros_like(v), v).to(t.float32)
+        return self._chunks(n, 4, one)
+
+    def prob_rows(self, rows, cols):
+        t = self.t
+        out = t.empty((rows, cols), dtype=t.float32, device=self.device)
+        step = max(1, self._CHUNK // cols)
+        for lo in range(0, rows, step):
+            hi = min(rows, lo + step)
+            u = self._u01_of(self.next((hi - lo) * cols)).view(hi - lo, cols) + 1.0 / 33554432.0
+            s = t.zeros(hi - lo, dtype=t.float64, device=self.device)
+            for c in range(cols):        # sequential sum, the order is part of the recipe
+                s = s + u[:, c]
+            out[lo:hi] = (u / s[:, None]).to(t.float32)
+        return out.view(-1)
+
+
+def config3_device(device, n=4096):
+    """Configuration 3's operands generated on `device` (same bits as config3())."""
+    g = DeviceRng(3, device)
+    return g.wide_mixed(n * n), g.wide_mixed(n * n)
+
+
+def config4_device(device, n=16384, a_rows=None, b_rows=None):
+    """Configuration 4's operands generated on `device`.  a_rows / b_rows = (lo, hi) restrict the result
+    to that block of rows of A / B (the stream is advanced past the rest), otherwise the whole matrix."""
+    g = DeviceRng(4, device)
+
+    def rows(block):
+        lo, hi = block if block is not None else (0, n)
+        g.skip(lo * n)
+        x = g.uniform_pm1((hi - lo) * n)
+        g.skip((n - hi) * n)
+        return x
+    return rows(a_rows), rows(b_rows)
+
+
+def config4_device_k_range(device, n, klo, khi):
+    """A[:, klo:khi] (as a dense n x (khi-klo) matrix) and B[klo:khi, :] of configuration 4 on `device`."""
+    t_ = DeviceRng(4, device)
+    torch = t_.t
+    A = torch.empty((n, khi - klo), dtype=torch.float32, device=t_.device)
+    step = max(1, DeviceRng._CHUNK // n)
+    for lo in range(0, n, step):                     # whole rows are drawn, the K range is kept
+        hi = min(n, lo + step)
+        A[lo:hi] = t_.uniform_pm1((hi - lo) * n).view(hi - lo, n)[:, klo:khi]
+    t_.skip(klo * n)
+    B = t_.uniform_pm1((khi - klo) * n)
+    return A.reshape(-1), B
+
+
+def config5_device(device, batch=96, T=1024, HD=64):
+    g = DeviceRng(5, device)
+    Q = g.normal(batch * T * HD)
+    Km = g.normal(batch * T * HD)
+    V = g.normal(batch * T * HD)
+    P = g.prob_rows(batch * T, T)
+    return Q, Km, V, P

@@ -132,6 +132,15 @@ def repro_gemm_fp32_batched_ws(A, B, Cout, M, N, K, batch, stride_a, stride_b, s
                                                  _stream(stream), _events(stage_events))
 
 
+def static_status():
+    """Status word of the fixed array behind repro_gemm_fp32_static (0, or the code of an expired wait)."""
+    st = C.c_int(0)
+    rc = _lib.lib().rgb200_static_status(C.byref(st))
+    if rc != cudaSuccess:
+        raise ReproGemmError(rc, "static_status")
+    return st.value
+
+
 def workspace_status(workspace):
     st = C.c_int(0)
     rc = _lib.lib().rgb200_workspace_status(_ptr(workspace), C.byref(st))
@@ -199,69 +208,56 @@ def gemm_batched(A, B, batch, M, N, K, trans_a=False, trans_b=False, slices=3):
 
 
 class HostGemm:
-    """C = op(A) op(B) for operands and result in pinned HOST memory, with the PCIe copies overlapped.
+    """C = op(A) op(B) for operands and result in pinned HOST memory, with the PCIe copies overlapped:
+    the Python face of rgb200_host_gemm_create / rgb200_gemm_fp32_host / rgb200_host_gemm_destroy.
 
-    B is copied first; A then travels in blocks of rows, and for each block the split pre-pass, the MMA
-    kernel and the copy of the finished rows of C back to the host run while the next block of A is
-    still on its way (three streams: copy-in, compute, copy-out).  Row blocks are independent
-    products (row scales and sums never cross rows), so the bits equal those of one call.
-    Device buffers, the workspace, streams and events are created once; a call allocates nothing.
-    With trans_a the rows of op(A) are not contiguous in host memory and the call falls back to
-    one copy, one run, one copy."""
+    The library copies B first; A then travels in blocks of rows, and for each block the split pre-pass,
+    the MMA kernel and the copy of the finished rows of C back to the host run while the next block of A
+    is still on its way.  Row blocks are independent products, so the bits equal those of one call.
+    Device buffers, workspace, streams and events are created once; a call allocates nothing."""
 
     def __init__(self, M, N, K, cfg=None, block_rows=512, device=None):
         self.M, self.N, self.K, self.cfg = M, N, K, cfg or Config()
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-        self.block = M if self.cfg.trans_a else max(1, min(block_rows, M))
-        self.blocks = [(lo, min(M, lo + self.block)) for lo in range(0, M, self.block)]
-        ws_bytes, self.blocks_with_k_ranges = 0, 0
-        for rows in {hi - lo for lo, hi in self.blocks}:       # a short block may plan K ranges of its own
-            rc, plan = make_plan(rows, N, K, self.cfg)
-            if rc != cudaSuccess:
-                raise ReproGemmError(rc, "make_plan")
-            ws_bytes = max(ws_bytes, plan.workspace_bytes)
-            if plan.split_k > 1:                               # those blocks launch one more kernel (the reduction)
-                self.blocks_with_k_ranges += sum(1 for lo, hi in self.blocks if hi - lo == rows)
+        self._h = C.c_void_p()
+        c = self.cfg.c()
         with torch.cuda.device(self.device):
-            self.dA = torch.empty(M * K, dtype=torch.float32, device=self.device)
-            self.dB = torch.empty(K * N, dtype=torch.float32, device=self.device)
-            self.dC = torch.empty(M * N, dtype=torch.float32, device=self.device)
-            self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
-            self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
-            self.ev_b = torch.cuda.Event()
-            self.ev_a = [torch.cuda.Event() for _ in self.blocks]
-            self.ev_c = [torch.cuda.Event() for _ in self.blocks]
+            rc = _lib.lib().rgb200_host_gemm_create(M, N, K, C.byref(c), block_rows, C.byref(self._h))
+        if rc != cudaSuccess:
+            raise ReproGemmError(rc, "host_gemm_create")
+        nb, nl, nbytes = C.c_int(0), C.c_int(0), C.c_size_t(0)
+        _lib.lib().rgb200_host_gemm_info(self._h, C.byref(nb), C.byref(nl), C.byref(nbytes))
+        self.blocks, self.launches, self.device_bytes = nb.value, nl.value, nbytes.value
 
-    def __call__(self, hA, hB, hC):
-        """Enqueues the whole product; on return the caller's current stream is ordered after the last
-        copy into hC (synchronise that stream, or record an event on it, to know when hC is ready)."""
-        M, N, K = self.M, self.N, self.K
-        cur = torch.cuda.current_stream(self.device)
-        for st in (self.s_in, self.s_run, self.s_out):
-            st.wait_stream(cur)
-        hA, hB, hC = hA.view(-1), hB.view(-1), hC.view(-1)
-        with torch.cuda.stream(self.s_in):
-            self.dB.copy_(hB, non_blocking=True)
-            self.ev_b.record()
-            for (lo, hi), ev in zip(self.blocks, self.ev_a):
-                self.dA[lo * K:hi * K].copy_(hA[lo * K:hi * K], non_blocking=True)
-                ev.record()
-        with torch.cuda.stream(self.s_run):
-            self.s_run.wait_event(self.ev_b)
-            for (lo, hi), ev_a, ev_c in zip(self.blocks, self.ev_a, self.ev_c):
-                self.s_run.wait_event(ev_a)
-                rc = repro_gemm_fp32_ws(self.dA[lo * K:hi * K], self.dB, self.dC[lo * N:hi * N], hi - lo, N, K, self.cfg,
-                                        self.ws, stream=self.s_run)
-                if rc != cudaSuccess:
-                    raise ReproGemmError(rc, "repro_gemm_fp32_ws")
-                ev_c.record()
-        with torch.cuda.stream(self.s_out):
-            for (lo, hi), ev_c in zip(self.blocks, self.ev_c):
-                self.s_out.wait_event(ev_c)
-                hC[lo * N:hi * N].copy_(self.dC[lo * N:hi * N], non_blocking=True)
-        cur.wait_stream(self.s_out)
-        cur.wait_stream(self.s_in)
-        cur.wait_stream(self.s_run)
+    def __call__(self, hA, hB, hC, stream=None):
+        """Enqueues the whole product; on return the stream (default: torch's current one) is ordered after
+        the last copy into hC: synchronise it, or record an event on it, to know when hC is ready."""
+        for t, n, name in ((hA, self.M * self.K, "A"), (hB, self.K * self.N, "B"), (hC, self.M * self.N, "C")):
+            if t.is_cuda or t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
+                raise ValueError("%s must be a contiguous float32 host tensor of %d elements" % (name, n))
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().rgb200_gemm_fp32_host(self._h, _ptr(hA), _ptr(hB), _ptr(hC), _stream(stream))
+        if rc != cudaSuccess:
+            raise ReproGemmError(rc, "gemm_fp32_host")
+
+    def status(self):
+        st = C.c_int(0)
+        rc = _lib.lib().rgb200_host_gemm_status(self._h, C.byref(st))
+        if rc != cudaSuccess:
+            raise ReproGemmError(rc, "host_gemm_status")
+        return st.value
+
+    def close(self):
+        if self._h:
+            with torch.cuda.device(self.device):
+                _lib.lib().rgb200_host_gemm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 # ------------------------------------------------------------------------------------------------

@@ -126,6 +126,29 @@ int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* 
                                    long long total_k, const rgb200_config* cfg, void* workspace,
                                    size_t workspace_bytes, void* stream);
 
+/* Host-buffer form: A, B and C live in HOST memory (pinned memory for the copies to overlap; pageable
+ * memory works but serialises).  It stands in for the sequence the reference's tools run around every
+ * product - cudaMemcpy of A and B, repro_gemm_fp32, cudaMemcpy of C
+ * (repro_gemm_cuda/hash_repro_gemm.cu:117-118,139; test_repro_gemm.cu:35-44) - as one pipelined call:
+ * B is copied first, A follows in blocks of rows, and for every block the split pre-pass, the MMA kernel
+ * and the copy of the finished rows of C back to the host overlap the transfer of the next block.
+ * Row blocks are independent products, so the result has the bits of a single call.
+ *   rgb200_host_gemm_create   allocates the device copies of A, B, C, the workspace, three streams and the
+ *                             events for one (M, N, K, cfg) on the current device; block_rows <= 0 picks 512.
+ *   rgb200_gemm_fp32_host     enqueues one product; allocates nothing and does not synchronise.  Work starts
+ *                             after what is already enqueued on `stream`, and `stream` continues after the
+ *                             last byte of C has landed: synchronise it (or record an event on it) before
+ *                             reading C_host.  One call at a time per handle.
+ *   rgb200_host_gemm_info     number of row blocks, kernels launched per call, device bytes held.
+ *   rgb200_host_gemm_status   after synchronising: 0, or the code of an expired bounded wait (see below).
+ *   rgb200_host_gemm_destroy  synchronises the device and frees everything. */
+typedef struct rgb200_host_gemm rgb200_host_gemm;
+int rgb200_host_gemm_create(int M, int N, int K, const rgb200_config* cfg, int block_rows, rgb200_host_gemm** handle);
+int rgb200_gemm_fp32_host(rgb200_host_gemm* handle, const float* A_host, const float* B_host, float* C_host, void* stream);
+int rgb200_host_gemm_info(const rgb200_host_gemm* handle, int* blocks, int* launches, size_t* device_bytes);
+int rgb200_host_gemm_status(const rgb200_host_gemm* handle, int* status);
+int rgb200_host_gemm_destroy(rgb200_host_gemm* handle);
+
 /* Call after the stream has been synchronised.  *status = 0 if the last run that used this workspace
  * completed, else the code a kernel left when one of its bounded waits expired (it then stopped
  * without hanging; the output is incomplete).  The reference reports kernel failures only through
@@ -166,6 +189,10 @@ int rgb200_selftest_bounded_wait(long long limit_clocks, int* status, long long*
 #define RGB200_STATIC_WORKSPACE_BYTES (32u << 20)
 int rgb200_gemm_fp32_static(const float* A, const float* B, float* C, int M, int N, int K,
                             const rgb200_config* cfg, void* stream);
+/* The counterpart of rgb200_workspace_status for the fixed array (its callers hold no workspace pointer):
+ * after synchronising the stream, *status = 0 if the last rgb200_gemm_fp32_static run on the current device
+ * completed, else the code of the bounded wait that expired. */
+int rgb200_static_status(int* status);
 
 /* ------------------------------------------------------------------------------------------------
  * 2-D convolution and its two gradients in PyTorch layouts (x[N,C,H,W], weight[F,C,KH,KW], output and

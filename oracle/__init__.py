@@ -25,14 +25,27 @@ REF_HASH_TOOL = os.path.join(_HERE, "_ref", "hash_repro_gemm_rgb200")
 FNV_OFFSET = 0xCBF29CE484222325
 
 
+def reference_root():
+    """Where a checkout of the reference project lives: $REPRO_REFERENCE_ROOT, else a directory named
+    ``reference`` beside this repository; None when neither holds the GEMM sources."""
+    for cand in (os.environ.get("REPRO_REFERENCE_ROOT"), os.path.join(_HERE, "..", "..", "reference")):
+        if cand and os.path.isfile(os.path.join(cand, "repro_gemm_cuda", "repro_gemm_cpu.h")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build(force=False):
     """Compile the checkers with oracle/Makefile (the reference build only where its sources exist)."""
     if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
         subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True, capture_output=True)
+    root = reference_root()
+    if root is None:
+        return                      # keep whatever was built where the sources were present
+    ref_arg = "REF_ROOT=" + root
     if force or not os.path.exists(_REF) or not os.path.exists(_REF_CONV):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, "ref", ref_arg], check=True, capture_output=True)
     if force or not os.path.exists(_REF_CUDA) or not os.path.exists(REF_CONV_TEST_TOOL):
-        subprocess.run(["make", "-C", _HERE, "ref_gpu"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, "ref_gpu", ref_arg], check=True, capture_output=True)
 
 
 def _f32(a):

@@ -160,6 +160,21 @@ def c4(path):
         json.dump(recs, f, indent=0)
 
 
+def kcat(path):
+    """Configuration 3's operands repeated w times along K (A = [A0 A0 ...], B = [B0; B0; ...]): the product a
+    K-sharded run forms when each of w ranks holds one K range.  Appends records c3.4096.kcat<w>."""
+    recs = [r for r in json.load(open(path)) if ".kcat" not in r["name"]]
+    n = 4096
+    c = fx.config3(n)[0]
+    A0, B0 = c["A"].reshape(n, n), c["B"].reshape(n, n)
+    for w in (2, 4, 8):
+        A = np.ascontiguousarray(np.tile(A0, (1, w))).reshape(-1)
+        B = np.ascontiguousarray(np.tile(B0, (w, 1))).reshape(-1)
+        recs.append(entry("c3.4096.kcat%d" % w, A, B, n, n, n * w, False, False, 3, "config3(4096) tiled %d times along K" % w)[0])
+    with open(path, "w") as f:
+        json.dump(recs, f, indent=0)
+
+
 def conv_hashes():
     """Forward, weight-gradient and input-gradient hashes from repro_conv_cuda/repro_conv_cpu.h:25,45,72."""
     recs = []
@@ -189,6 +204,8 @@ if __name__ == "__main__":
         gemm_hashes(path)
     if what == "c4":
         c4(path)
+    if what == "kcat":
+        kcat(path)
     if what in ("conv", "all"):
         if oracle.ref_conv() is None:
             sys.exit("the reference library oracle/_ref/librepro_ref_conv.so could not be built here")

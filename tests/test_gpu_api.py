@@ -238,7 +238,8 @@ def test_suite_tool_writes_reference_format(tmp_path):
 
 def test_host_buffer_pipeline_matches_single_call():
     """Pinned host operands in, pinned host result out, row blocks overlapped with the copies: same bits
-    as one call, for plain and transposed storage (the latter falls back to a single block)."""
+    as one call, for plain and transposed storage (a row block of a transposed A is a band of columns of the
+    stored matrix and travels as a pitched copy)."""
     M, N, K = 1100, 260, 520
     A, B = fx.hash_tool_inputs("wide", M, N, K)
     want = oracle.gemm(A, B, M, N, K)
@@ -252,11 +253,16 @@ def test_host_buffer_pipeline_matches_single_call():
             torch.cuda.synchronize()
             assert np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1)), block_rows
     hAt = torch.from_numpy(np.ascontiguousarray(A.reshape(M, K).T).reshape(-1)).pin_memory()
-    pipe = rg.HostGemm(M, N, K, rg.Config(trans_a=True))
-    hC.fill_(float("nan"))
-    pipe(hAt, hB, hC)
-    torch.cuda.synchronize()
-    assert len(pipe.blocks) == 1 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
+    hBt = torch.from_numpy(np.ascontiguousarray(B.reshape(K, N).T).reshape(-1)).pin_memory()
+    for cfg, a, b in ((rg.Config(trans_a=True), hAt, hB), (rg.Config(trans_a=True, trans_b=True), hAt, hBt),
+                      (rg.Config(trans_b=True), hA, hBt)):
+        pipe = rg.HostGemm(M, N, K, cfg)
+        hC.fill_(float("nan"))
+        pipe(a, b, hC)
+        torch.cuda.synchronize()
+        assert pipe.blocks == 3 and pipe.status() == 0
+        assert np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1)), cfg
+        pipe.close()
 
 
 def test_host_buffer_pipeline_short_last_block_with_own_k_ranges():
@@ -271,7 +277,9 @@ def test_host_buffer_pipeline_short_last_block_with_own_k_ranges():
     pipe = rg.HostGemm(M, N, K, rg.Config(), block_rows=512)
     pipe(hA, hB, hC)
     torch.cuda.synchronize()
-    assert len(pipe.blocks) == 2 and pipe.blocks_with_k_ranges == 1 and np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
+    # kernels per call: B's two pre-pass kernels once, A's split + MMA per block, one K-range reduction for the short block
+    assert pipe.blocks == 2 and pipe.launches == 2 + 2 + 3
+    assert np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
 
 
 def test_bounded_wait_expires_and_reports():

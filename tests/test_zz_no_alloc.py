@@ -5,7 +5,7 @@ operator under a framework's caching allocator, a latency-critical step that mus
 device-wide synchronisation of cudaMalloc / cudaFree).  Its scratch is a fixed array inside the
 library that every call shares and that keeps the previous call's contents, so the checks below run
 two calls in a row, of different shapes, and compare each with the ordinary workspace entry point
-bit for bit.  This file is collected last on purpose: a run that stops at the first failure has
+and with the CPU oracle bit for bit.  This file is collected last on purpose: a run that stops at the first failure has
 then already exercised everything else.
 """
 import ctypes as C
@@ -13,6 +13,8 @@ import ctypes as C
 import numpy as np
 import pytest
 import torch
+
+import oracle
 
 from bit_reproducible_training_b200 import _lib
 from bit_reproducible_training_b200 import fixtures as fx
@@ -52,12 +54,16 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point():
              (700, 520, 1300, rg.Config(slices=3))]
     g = fx.Rng(2718)
     for M, N, K, cfg in cases:
-        A = torch.from_numpy(g.wide(M * K, -12, 12)).cuda()
-        B = torch.from_numpy(g.normal(K * N)).cuda()
+        hA, hB = g.wide(M * K, -12, 12), g.normal(K * N)
+        A, B = torch.from_numpy(hA).cuda(), torch.from_numpy(hB).cuda()
         want = with_workspace(A, B, M, N, K, cfg)
+        cpu = oracle.gemm(hA, hB, M, N, K, cfg.trans_a, cfg.trans_b, cfg.slices)
+        assert np.array_equal(want.cpu().numpy().view(np.uint32), cpu.view(np.uint32)), (M, N, K)
         for _ in range(2):
             got = through_static(A, B, M, N, K, cfg)
             assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (M, N, K)
+            assert np.array_equal(got.cpu().numpy().view(np.uint32), cpu.view(np.uint32)), (M, N, K)
+            assert rg.static_status() == 0
 
 
 def test_problems_beyond_the_fixed_array_are_refused_cleanly():
