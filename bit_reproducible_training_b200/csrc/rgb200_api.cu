@@ -15,7 +15,10 @@
 #include "../../include/rgb200.h"
 #include "rgb200_math.cuh"
 #include "rgb200_mma.cuh"
+#include "rgb200_smallk.cuh"
+#include "rgb200_rowfused.cuh"
 #include "rgb200_prepass.cuh"
+#include "rgb200_prepass_cluster.cuh"
 #include "rgb200_conv.cuh"
 
 namespace rgb200 {
@@ -140,8 +143,6 @@ cudaError_t plan_layout(int M, int N, int K, long long total_k, int batch, const
 // ------------------------------------------------------------------------------------------
 struct DeviceInfo {
     int sm_count = 0; int cc = 0; bool attrs_set = false; cudaError_t err = cudaSuccess;
-    // side stream and events for running the two operands' pre-passes next to each other
-    cudaStream_t side = nullptr; cudaEvent_t fork_ev = nullptr, join_ev = nullptr; mutable std::mutex fork_mutex;
 };
 DeviceInfo g_dev[MAX_DEVICES];
 std::once_flag g_dev_once[MAX_DEVICES];
@@ -150,6 +151,15 @@ template <int S, int NT, bool IMAGE_MAJOR_C = false>
 cudaError_t set_kernel_attrs() {
     return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<S, NT, IMAGE_MAJOR_C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 GemmTraits<S, NT>::SMEM_BYTES);
+}
+
+template <int S>
+cudaError_t set_cluster_split_attrs() {
+    const int bytes = KSC_MAX_SLAB_BYTES + 128;
+    cudaError_t e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e;
 }
 
 cudaError_t device_info(const DeviceInfo** out) {
@@ -176,13 +186,24 @@ cudaError_t device_info(const DeviceInfo** out) {
                 d.err = e2;
                 return;
             }
-            d.attrs_set = true;
-            if (cudaStreamCreateWithFlags(&d.side, cudaStreamNonBlocking) != cudaSuccess ||
-                cudaEventCreateWithFlags(&d.fork_ev, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&d.join_ev, cudaEventDisableTiming) != cudaSuccess) {
-                d.side = nullptr;             // the pre-passes then simply run one after the other
-                (void)cudaGetLastError();
+            if ((e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<1>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<2>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<3>::SMEM_BYTES)) != cudaSuccess) {
+                d.err = e2;
+                return;
             }
+            if ((e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<1>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<2>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<3>::SMEM_BYTES)) != cudaSuccess) {
+                d.err = e2;
+                return;
+            }
+            if ((e2 = set_cluster_split_attrs<1>()) != cudaSuccess || (e2 = set_cluster_split_attrs<2>()) != cudaSuccess ||
+                (e2 = set_cluster_split_attrs<3>()) != cudaSuccess) {
+                d.err = e2;
+                return;
+            }
+            d.attrs_set = true;
         }
     });
     if (g_dev[dev].err != cudaSuccess) return g_dev[dev].err;
@@ -210,7 +231,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn g_encode = nullptr;
 std::once_flag g_encode_once;
 
-cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, int Kp, int S, int batch, int box_rows) {
+bool ensure_encode() {
     std::call_once(g_encode_once, [] {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qr;
@@ -218,7 +239,11 @@ cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, in
             qr == cudaDriverEntryPointSuccess)
             g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     });
-    if (!g_encode) return cudaErrorNotSupported;
+    return g_encode != nullptr;
+}
+
+cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, int Kp, int S, int batch, int box_rows) {
+    if (!ensure_encode()) return cudaErrorNotSupported;
     // dims (fastest first): k, row, digit plane, batch.  Rows beyond `rows` read as zero.
     cuuint64_t dims[4] = {(cuuint64_t)Kp, (cuuint64_t)rows, (cuuint64_t)S, (cuuint64_t)batch};
     cuuint64_t strides[3] = {(cuuint64_t)Kp, (cuuint64_t)rows * Kp, (cuuint64_t)rows * Kp * S};
@@ -228,6 +253,48 @@ cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, in
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// FP32 operand stored [batch][K][R] (r contiguous), as the cluster split reads it: dims (r, k, batch), box (W, 64, 1).
+cudaError_t encode_kstrided_map(CUtensorMap* map, const float* src, int R, int K, int batch, long long batch_stride, int W) {
+    if (!ensure_encode()) return cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)K, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)R * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)R * K) * 4};
+    cuuint32_t box[3] = {(cuuint32_t)W, (cuuint32_t)KSC_BOX_K, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(src), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// The cluster form of the k-strided split (one read of the operand).  Returns false when the operand cannot
+// take it (rows not a multiple of four floats, unaligned base or batch stride, K too long for a slab), and the
+// caller then runs the two-kernel form.
+template <int S, int W>
+void launch_cluster_split(const CUtensorMap& map, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp,
+                          int KC, int batch, int* status, cudaStream_t st) {
+    const size_t smem = (size_t)KC * W * 4 + 128;
+    split_kstrided_cluster_kernel<S, W><<<dim3(KSC_CLUSTER * ceil_div(R, W), batch), PREPASS_THREADS, smem, st>>>(
+        map, given_max, planes, expo, R, K, Kp, KC, status);
+}
+
+template <int S>
+bool try_cluster_split(const float* src, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp, int batch,
+                       long long batch_stride, int* status, cudaStream_t st) {
+    if (R % 4 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (batch > 1 && batch_stride % 4 != 0)) return false;
+    if (!ensure_encode()) return false;
+    const int KC = ceil_div(ceil_div(Kp, KSC_CLUSTER), KSC_BOX_K) * KSC_BOX_K;
+    int W = 32;
+    while (W > 8 && (size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) W >>= 1;
+    if ((size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) return false;
+    while (W > 8 && (long long)ceil_div(R, W) * KSC_CLUSTER * batch < PLAN_SM_COUNT) W >>= 1;   // few columns: narrower panels, more CTAs
+    CUtensorMap map;
+    if (encode_kstrided_map(&map, src, R, K, batch, batch_stride, W) != cudaSuccess) return false;
+    if (W == 32) launch_cluster_split<S, 32>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, st);
+    else if (W == 16) launch_cluster_split<S, 16>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, st);
+    else launch_cluster_split<S, 8>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, st);
+    return true;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -270,11 +337,13 @@ void launch_kmajor(const KmajorOperand& first, const KmajorOperand& second, int 
 // One operand through the pre-pass.  k_major: element (r, k) at src[r*K + k].
 template <int S>
 void launch_split(const float* src, bool k_major, const float* given_max, uint32_t* maxbits, int8_t* planes, int* expo,
-                  int R, int K, int Kp, int batch, long long batch_stride, cudaStream_t st) {
+                  int R, int K, int Kp, int batch, long long batch_stride, int* status, cudaStream_t st) {
     if (k_major) {
         const KmajorOperand op{src, given_max, planes, expo, R, batch_stride};
         const KmajorOperand none{nullptr, nullptr, nullptr, nullptr, 0, 0};
         launch_kmajor<S>(op, none, K, Kp, batch, nullptr, st);
+    } else if (try_cluster_split<S>(src, given_max, planes, expo, R, K, Kp, batch, batch_stride, status, st)) {
+        // one read of the operand; the zeroed maxima words stay unused
     } else {
         if (given_max)
             maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);
@@ -346,9 +415,36 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     const int e0 = -14 * (S - 1);
 
     cudaError_t e = cudaSuccess;
+    // Skinny output (N <= 64) with a k-contiguous A: A's split is fused into the MMA kernel's producer and its
+    // digit planes never reach HBM (rgb200_rowfused.cuh); only B goes through the pre-pass.
+    const bool fused_a = !a.hook && !a.trans_a && !a.max_a && !part && !a.scatter && !a.c_image_rows &&
+                         L.algo == RGB200_ALGO_TENSORCORE && L.N <= RF_NT && L.split == 1 && L.k_blocks > 1 &&
+                         L.K % 4 == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 && (L.batch == 1 || a.stride_a % 4 == 0);
     // Both operands k-contiguous (the forward product of a linear layer, C = A B^T): one launch splits both
     // and clears the status word; no column maxima are needed, hence no memset either.
     const bool both_kmajor = !a.trans_a && a.trans_b;
+    if (fused_a) {
+        if (!a.reuse_b) {
+            if ((e = cudaMemsetAsync(a.ws, 0, L.zero_b_bytes, a.st)) != cudaSuccess) return e;   // status word + column maxima of B
+            record(0);
+            launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, status, a.st);
+        } else {
+            record(0);
+        }
+        record(1);
+        CUtensorMap map_b;
+        if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, RF_NT)) != cudaSuccess) return e;
+        RowFusedParams Q;
+        Q.A = a.A; Q.stride_a = a.stride_a; Q.expo_b = eb; Q.C = a.C; Q.status = status;
+        Q.M = L.M; Q.N = L.N; Q.K = L.K; Q.batch = L.batch; Q.stride_c = a.stride_c;
+        Q.m_tiles = ceil_div(L.M, BLOCK_M); Q.k_blocks = L.k_blocks; Q.e0 = e0;
+        const long long rf_tiles = (long long)L.batch * Q.m_tiles;
+        const int rf_grid = (int)(rf_tiles < dev.sm_count ? rf_tiles : dev.sm_count);
+        gemm_i8_rowfused_kernel<S><<<rf_grid, RF_THREADS, RowFusedTraits<S>::SMEM_BYTES, a.st>>>(map_b, Q);
+        record(2);
+        record(3);
+        return cudaGetLastError();
+    }
     if (a.hook) {
         if ((e = cudaMemsetAsync(a.ws, 0, L.zero_b_bytes, a.st)) != cudaSuccess) return e;
         if ((e = cudaMemsetAsync(a.ws + L.max_a, 0, L.zero_a_bytes, a.st)) != cudaSuccess) return e;
@@ -359,7 +455,7 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         // B's planes and exponents are those of the previous call on this workspace (same N, K, S): only A is split
         if (a.trans_a && (e = cudaMemsetAsync(a.ws + L.max_a, 0, L.zero_a_bytes, a.st)) != cudaSuccess) return e;
         record(0);
-        launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, a.st);
+        launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, status, a.st);
         record(1);
     } else if (both_kmajor) {
         record(0);
@@ -371,25 +467,10 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         if ((e = cudaMemsetAsync(a.ws, 0, L.zero_b_bytes, a.st)) != cudaSuccess) return e;   // status word + column maxima of B
         if (a.trans_a && (e = cudaMemsetAsync(a.ws + L.max_a, 0, L.zero_a_bytes, a.st)) != cudaSuccess) return e;
         record(0);
-        // The two operands are independent until the MMA kernel.  For large operands A's split runs on a side
-        // stream next to B's (fork and join by events, so the caller's stream still orders everything; this
-        // also holds inside a stream capture).  cudaStreamWaitEvent binds to the record made just before it,
-        // and the mutex keeps another host thread from re-recording the shared event in between.
-        const bool fork = dev.side != nullptr && (double)L.batch * L.K * ((double)L.M + L.N) >= 8.0e6;
-        bool forked = false;
-        if (fork) {
-            std::lock_guard<std::mutex> lock(dev.fork_mutex);
-            forked = cudaEventRecord(dev.fork_ev, a.st) == cudaSuccess &&
-                     cudaStreamWaitEvent(dev.side, dev.fork_ev, 0) == cudaSuccess;
-            if (!forked) (void)cudaGetLastError();
-        }
-        launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, forked ? dev.side : a.st);
-        launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, a.st);
-        if (forked) {
-            std::lock_guard<std::mutex> lock(dev.fork_mutex);
-            if (cudaEventRecord(dev.join_ev, dev.side) != cudaSuccess || cudaStreamWaitEvent(a.st, dev.join_ev, 0) != cudaSuccess)
-                return cudaErrorUnknown;          // the side stream could not be joined: do not run on half-ordered data
-        }
+        // both splits on the caller's stream, one after the other: each saturates the memory system by itself, and
+        // the library keeps no stream or event of its own
+        launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, status, a.st);
+        launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, status, a.st);
         record(1);
     }
 
@@ -402,8 +483,25 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     }
 
     if (a.c_image_rows && (L.split != 1 || L.batch != 1 || part)) return cudaErrorInvalidValue;
-    const int tile_n = a.c_image_rows ? TILE_N_BASE : tile_n_for(S, L.N);
     CUtensorMap map_a, map_b;
+    if (L.k_blocks == 1 && !part && !a.c_image_rows && !a.scatter) {
+        // the whole K fits one k block (attention scores and the like): the epilogue-centred kernel
+        if ((e = encode_planes_map(&map_a, qa, L.M, L.Kp, S, L.batch, BLOCK_M)) != cudaSuccess) return e;
+        if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, SK_NT)) != cudaSuccess) return e;
+        SmallKParams Q;
+        Q.expo_a = ea; Q.expo_b = eb; Q.C = a.C; Q.status = status;
+        Q.M = L.M; Q.N = L.N; Q.batch = L.batch; Q.stride_c = a.stride_c;
+        Q.m_tiles = ceil_div(L.M, BLOCK_M); Q.n_tiles = ceil_div(L.N, SK_NT);
+        Q.k_steps = ceil_div(L.K, UMMA_K);
+        Q.e0 = e0;
+        const long long sk_tiles = (long long)L.batch * Q.m_tiles * Q.n_tiles;
+        const int sk_grid = (int)(sk_tiles < dev.sm_count ? sk_tiles : dev.sm_count);
+        gemm_i8_smallk_kernel<S><<<sk_grid, SK_THREADS, SmallKTraits<S>::SMEM_BYTES, a.st>>>(map_a, map_b, Q);
+        record(2);
+        record(3);
+        return cudaGetLastError();
+    }
+    const int tile_n = a.c_image_rows ? TILE_N_BASE : tile_n_for(S, L.N);
     if ((e = encode_planes_map(&map_a, qa, L.M, L.Kp, S, L.batch, BLOCK_M)) != cudaSuccess) return e;
     if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, tile_n)) != cudaSuccess) return e;
     GemmParams P;

@@ -1,0 +1,330 @@
+// Skinny-output variant of the tcgen05 kind::i8 kernel with the split of A fused into the producer
+// (N <= 64, A stored k-contiguous; the attention product P V with P [1024 x 1024] and V [1024 x 64] is
+// the case it was written for).
+//
+// For such a product A is nearly all of the traffic: staging its S digit planes in HBM, as the general
+// path does, writes and re-reads S bytes per element on top of the four that must be read.  Here a CTA
+// owns a 128-row block of A and never stores its planes:
+//   pass 1  sixteen warps stream the block's rows (16-byte loads, a warp per 512-byte row segment) and
+//           keep a running maximum per row; the row's scale exponent follows;
+//   pass 2  the same warps read the rows again (the block was just read, so most of it comes from L2),
+//           round to the fixed-point integer, split it into S digits and store them straight into the
+//           128-byte-swizzled shared-memory image the MMA reads - the layout TMA would have produced -
+//           one k block (128 values per row) per pipeline stage;
+//   MMA     one thread issues the same level-accumulating MMAs as the general kernel, against B's digit
+//           planes, which are small and still come from HBM/L2 by TMA;
+//   finish  the sixteen warps drain TMEM, rebuild the exact sums, round once and store C.
+// The arithmetic is that of the general kernel (rgb200_mma.cuh) and of the split pre-pass
+// (rgb200_prepass.cuh); only where the digits of A live differs.  Reference counterparts:
+// quantize_kmajor + gemm_wmma_i8 (repro_gemm_cuda/repro_gemm.cu:54-79, 280-364).
+#pragma once
+#include "rgb200_mma.cuh"
+#include "rgb200_prepass.cuh"
+#include "rgb200_smallk.cuh"
+
+namespace rgb200 {
+
+constexpr int RF_NT = 64;                     // columns of C per tile (one tile covers all of N)
+constexpr int RF_A_STAGES = 3;
+constexpr int RF_B_STAGES = 3;
+constexpr int RF_WORK_WARPS = 16;             // converter + epilogue warps
+constexpr int RF_WORK_THREADS = RF_WORK_WARPS * 32;
+constexpr int RF_THREADS = 64 + RF_WORK_THREADS;      // 576
+constexpr int RF_ROWS_PER_WARP = BLOCK_M / RF_WORK_WARPS;   // 8
+
+template <int S>
+struct RowFusedTraits {
+    static constexpr int LEVELS = 2 * S - 1;
+    static constexpr int A_PLANE_BYTES = BLOCK_M * BLOCK_K;
+    static constexpr int A_STAGE_BYTES = S * A_PLANE_BYTES;
+    static constexpr int B_PLANE_BYTES = RF_NT * BLOCK_K;
+    static constexpr int B_STAGE_BYTES = S * B_PLANE_BYTES;
+    static constexpr int ACC_COLS = LEVELS * RF_NT;
+    static constexpr int TMEM_COLS = ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int CPT = RF_NT / 4;     // sixteen columns per epilogue thread
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = RF_A_STAGES * A_STAGE_BYTES + RF_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
+                                      RF_WORK_WARPS * CPT * 4 /* column exponents */ + BLOCK_M * 4 /* row exponents */;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+struct RowFusedParams {
+    const float* A;          // [batch][M][K], k contiguous
+    long long stride_a;      // elements between batches
+    const int* expo_b;       // [batch][N]
+    float* C;
+    int* status;
+    int M, N, K, batch;
+    long long stride_c;
+    int m_tiles, k_blocks;
+    int e0;
+};
+
+template <int S>
+__global__ void __launch_bounds__(RF_THREADS, 1)
+gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFusedParams P) {
+    using Tr = RowFusedTraits<S>;
+    constexpr int NT = RF_NT, CPT = Tr::CPT;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = smem_base + RF_A_STAGES * Tr::A_STAGE_BYTES;
+    const uint32_t bar_base = b_base + RF_B_STAGES * Tr::B_STAGE_BYTES;
+    auto a_full = [&](int s) { return bar_base + 8u * s; };
+    auto a_empty = [&](int s) { return bar_base + 8u * (RF_A_STAGES + s); };
+    auto b_full = [&](int s) { return bar_base + 8u * (2 * RF_A_STAGES + s); };
+    auto b_empty = [&](int s) { return bar_base + 8u * (2 * RF_A_STAGES + RF_B_STAGES + s); };
+    constexpr int NBAR = 2 * RF_A_STAGES + 2 * RF_B_STAGES;
+    const uint32_t tmem_full_bar = bar_base + 8u * NBAR;
+    const uint32_t tmem_empty_bar = bar_base + 8u * (NBAR + 1);
+    // two barriers among the sixteen work warps (one arrival per warp); waits on them are bounded like all others
+    const uint32_t rows_bar = bar_base + 8u * (NBAR + 2);       // every warp has published its rows' exponents
+    const uint32_t done_bar = bar_base + 8u * (NBAR + 3);       // every warp has finished the tile's epilogue
+    const uint32_t tmem_slot = bar_base + 8u * (NBAR + 4);
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint8_t* gen_a = gen_base;
+    uint8_t* gen_bar = gen_base + RF_A_STAGES * Tr::A_STAGE_BYTES + RF_B_STAGES * Tr::B_STAGE_BYTES;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_bar + 8 * (NBAR + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_bar + 8 * (NBAR + 5));
+    int* eb_slots = reinterpret_cast<int*>(gen_bar + Tr::BAR_BYTES);
+    int* ea_rows = eb_slots + RF_WORK_WARPS * CPT;        // scale exponents of the tile's 128 rows
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = P.batch * P.m_tiles;          // one tile per (batch, row block)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RF_A_STAGES; ++s) { mbar_init(a_full(s), RF_WORK_WARPS); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < RF_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+        mbar_init(tmem_full_bar, 1);
+        mbar_init(tmem_empty_bar, RF_WORK_THREADS);
+        mbar_init(rows_bar, RF_WORK_WARPS);
+        mbar_init(done_bar, RF_WORK_WARPS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Tr::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (B planes only)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int batch = tile / P.m_tiles;
+                for (int kb = 0; kb < P.k_blocks; ++kb, ++it) {
+                    const int s = it % RF_B_STAGES;
+                    if (!(ok = mbar_wait(b_empty(s), ((it / RF_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
+                    mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
+                    tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), kb * BLOCK_K, 0, 0, batch);
+                }
+            }
+            if (!ok) {
+                for (uint32_t j = 0; j < (it < (uint32_t)RF_B_STAGES ? it : (uint32_t)RF_B_STAGES); ++j) {
+                    const uint32_t i2 = it - 1 - j;
+                    long long c0 = clock64();
+                    while (!mbar_try_wait(b_full(i2 % RF_B_STAGES), (i2 / RF_B_STAGES) & 1u))
+                        if (clock64() - c0 > WAIT_LIMIT_CLOCKS) { atomicCAS(P.status, 0, STATUS_WAIT_DRAIN); break; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
+            constexpr uint32_t IDESC_ONE = idesc_i8(BLOCK_M, NT);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
+                if (!(ok = mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
+                tc_fence_after();
+                for (int kb = 0; kb < P.k_blocks; ++kb, ++it) {
+                    const int sa_i = it % RF_A_STAGES, sb_i = it % RF_B_STAGES;
+                    if (!(ok = mbar_wait(a_full(sa_i), (it / RF_A_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                    if (!(ok = mbar_wait(b_full(sb_i), (it / RF_B_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                    tc_fence_after();
+                    const uint32_t sa = a_base + sa_i * Tr::A_STAGE_BYTES;
+                    const uint32_t sb = b_base + sb_i * Tr::B_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        if (kb == 0 && k == 0) {
+#pragma unroll
+                            for (int p = 0; p < S; ++p)
+#pragma unroll
+                                for (int q = 0; q < S; ++q)
+                                    umma_i8(tmem_base + (p + q) * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES),
+                                            smem_desc_sw128(sb + q * Tr::B_PLANE_BYTES), IDESC_ONE, (p != 0 && q != S - 1) ? 1u : 0u);
+                        } else {
+#pragma unroll
+                            for (int p = 0; p < S; ++p)
+                                umma_i8(tmem_base + p * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES + k * UMMA_K),
+                                        smem_desc_sw128(sb + k * UMMA_K), IDESC_WIDE, 1u);
+                        }
+                    }
+                    umma_commit(a_empty(sa_i));
+                    umma_commit(b_empty(sb_i));
+                }
+                if (ok) umma_commit(tmem_full_bar);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- converters, then epilogue (warps 2..17)
+        using TAcc = typename std::conditional<S == 1, int, long long>::type;
+        constexpr int RPW = RF_ROWS_PER_WARP;
+        const int cw = warp - 2;
+        const int quarter = warp & 3;                  // TMEM lanes this warp may read
+        const int cgroup = cw >> 2;                    // which sixteen columns of the tile
+        int* eb_s = eb_slots + cw * CPT;
+        const int k_chunks = P.K >> 2;                 // float4 chunks per row (K % 4 == 0 is a launch condition)
+        uint32_t it = 0, tile_it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
+            const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
+            const int row0 = m_blk * BLOCK_M + cw * RPW;                       // this warp's first row
+            const float4* src = reinterpret_cast<const float4*>(P.A + (size_t)batch * P.stride_a + (size_t)row0 * P.K);
+            // pass 1: row maxima
+            float m[RPW];
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) m[i] = 0.0f;
+            for (int kb = 0; kb < P.k_blocks; ++kb) {
+                const int c = kb * 32 + lane;
+                float4 v[RPW];
+#pragma unroll
+                for (int i = 0; i < RPW; ++i)
+                    v[i] = (row0 + i < P.M && c < k_chunks) ? __ldg(src + (size_t)i * k_chunks + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < RPW; ++i) m[i] = abs4max(m[i], v[i]);
+            }
+            int e[RPW];
+            float f1[RPW];
+            bool all_plain = true;
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m[i] = fmaxf(m[i], __shfl_xor_sync(0xFFFFFFFFu, m[i], o));
+                e[i] = scale_exponent(m[i]);
+                f1[i] = quant_scale(e[i], S).f1;
+                all_plain = all_plain && plain_row(e[i]);
+            }
+            // the previous tile's epilogue has finished reading ea_rows (it ends with the barrier below)
+            if (lane < RPW) {
+                int ev = e[0];
+#pragma unroll
+                for (int i = 1; i < RPW; ++i) ev = lane == i ? e[i] : ev;
+                ea_rows[cw * RPW + lane] = ev;
+            }
+            // pass 2: digits into the swizzled stages
+            for (int kb = 0; kb < P.k_blocks; ++kb, ++it) {
+                const int c = kb * 32 + lane;
+                float4 v[RPW];
+#pragma unroll
+                for (int i = 0; i < RPW; ++i)
+                    v[i] = (row0 + i < P.M && c < k_chunks) ? __ldg(src + (size_t)i * k_chunks + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const int s = it % RF_A_STAGES;
+                ok = mbar_wait(a_empty(s), ((it / RF_A_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                uint8_t* stage = gen_a + s * Tr::A_STAGE_BYTES;
+#pragma unroll
+                for (int i = 0; i < RPW; ++i) {
+                    const int r = cw * RPW + i;                                 // row inside the tile
+                    // 128-byte rows, 16-byte chunks XOR-ed with the row index modulo 8: the 128-byte swizzle
+                    const size_t off = (size_t)r * 128 + ((((lane >> 2) ^ (r & 7))) << 4) + ((lane & 3) << 2);
+                    if (all_plain) {
+                        QuantScale q; q.f1 = f1[i]; q.f2 = 1.0f; q.lim = 0;
+                        store_quad_impl<S, true>(v[i], q, reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
+                    } else {
+                        store_quad<S>(v[i], quant_scale(e[i], S), plain_row(e[i]), reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(a_full(s));
+            }
+            if (!ok) break;
+            // every warp's row exponents are in ea_rows before any warp's epilogue reads them
+            __syncwarp();
+            if (lane == 0) mbar_arrive(rows_bar);
+            ok = mbar_wait(rows_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            // epilogue: 32 rows x 16 columns per warp
+            const int row_in_tile = quarter * 32 + lane;
+            const int row = m_blk * BLOCK_M + row_in_tile;
+            const bool row_ok = row < P.M;
+            const int col0 = cgroup * CPT;
+            if (lane < CPT) eb_s[lane] = col0 + lane < P.N ? __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane) : 0;
+            __syncwarp();
+            const int ea = ea_rows[row_in_tile];
+            ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + col0;
+            TAcc T[CPT];
+#pragma unroll
+            for (int c0 = 0; c0 < CPT; c0 += 8) {
+                int lv[Tr::LEVELS][8];
+#pragma unroll
+                for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    long long t = lv[Tr::LEVELS - 1][j];
+#pragma unroll
+                    for (int L = Tr::LEVELS - 2; L >= 0; --L)
+                        t += (long long)lv[L][j] * (long long)(1 << (7 * (Tr::LEVELS - 1 - L)));
+                    T[c0 + j] = (TAcc)t;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tmem_empty_bar);
+            if (row_ok && col0 < P.N) {
+                uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
+                const int ebase = ea + P.e0;
+                const bool whole = col0 + CPT <= P.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+#pragma unroll
+                for (int j = 0; j < CPT; j += 4) {
+                    uint32_t r[4];
+                    bool k0, k1, k2, k3;
+                    r[0] = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
+                    r[1] = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
+                    r[2] = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
+                    r[3] = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                    if (!(k0 && k1 && k2 && k3)) {
+                        r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
+                        r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
+                        r[2] = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
+                        r[3] = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
+                    }
+                    if (whole) {
+                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col0 + j + q < P.N) dst[j + q] = r[q];
+                    }
+                }
+            }
+            // ea_rows is rewritten by the next tile's first pass
+            __syncwarp();
+            if (lane == 0) mbar_arrive(done_bar);
+            ok = mbar_wait(done_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+        }
+    }
+
+    // common exit: every thread arrives, then the allocating warp returns the TMEM columns
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Tr::TMEM_COLS);
+    }
+}
+
+}  // namespace rgb200

@@ -1,0 +1,293 @@
+// Short-K variant of the tcgen05 kind::i8 kernel: the whole K extent fits one 128-byte k block
+// (K <= 128; the attention scores Q K^T with K = 64 are the case it was written for).
+//
+// With so little K the tensor pipe is idle most of the time and a tile's cost is its epilogue:
+// 2S-1 TMEM reads, the INT64 recombination, one rounding and four bytes of C per output.  The
+// general kernel cannot overlap that work with the next tile's MMAs at S = 3 (its 128 x 64 tile fills
+// 320 of the 512 TMEM columns), so this one is organised around the epilogue instead:
+//   * 128 x 32 tiles: the (2S-1) * 32 accumulator columns fit TMEM twice.  Two groups of eight
+//     epilogue warps own one accumulator set each and alternate tiles, so sixteen warps drain, round
+//     and store while the MMA warp is already one or two tiles ahead.
+//   * A-stationary: a CTA walks a contiguous range of tiles with the column tile running fastest, so
+//     the 128-row A tile (all S planes, the whole K) is loaded once per row of tiles into one of two
+//     buffers; only the small B tiles stream through a ring of stages.
+//   * k steps beyond K (zero padding of the 128-byte block) are not issued.
+// The arithmetic (level accumulators, exact INT64 sums, single rounding) is that of the general
+// kernel; see rgb200_mma.cuh.  Reference counterpart: gemm_wmma_i8<S> (repro_gemm_cuda/repro_gemm.cu:280-364);
+// the batched attention products it serves are listed as pending at gpt2_ops_suite/gpt2_ops_suite.cu:543-548.
+#pragma once
+#include "rgb200_mma.cuh"
+
+namespace rgb200 {
+
+constexpr int SK_NT = 32;                     // columns of C per tile
+constexpr int SK_B_STAGES = 6;
+constexpr int SK_EPI_GROUPS = 2;              // one per accumulator set
+constexpr int SK_GROUP_WARPS = 8;
+constexpr int SK_GROUP_THREADS = SK_GROUP_WARPS * 32;
+constexpr int SK_THREADS = 64 + SK_EPI_GROUPS * SK_GROUP_THREADS;    // 576
+
+// 32 lanes x 8 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+
+template <int S>
+struct SmallKTraits {
+    static constexpr int LEVELS = 2 * S - 1;
+    static constexpr int A_PLANE_BYTES = BLOCK_M * BLOCK_K;
+    static constexpr int A_BYTES = S * A_PLANE_BYTES;
+    static constexpr int B_PLANE_BYTES = SK_NT * BLOCK_K;
+    static constexpr int B_STAGE_BYTES = S * B_PLANE_BYTES;
+    static constexpr int ACC_COLS = LEVELS * SK_NT;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int CPT = SK_NT / 2;                    // columns per epilogue thread
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = 2 * A_BYTES + SK_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
+                                      SK_EPI_GROUPS * SK_GROUP_WARPS * CPT * 4;
+    static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit TMEM");
+    static_assert(CPT % 8 == 0, "the epilogue reads eight TMEM columns at a time");
+};
+
+struct SmallKParams {
+    const int* expo_a;       // [batch][M]
+    const int* expo_b;       // [batch][N]
+    float* C;
+    int* status;
+    int M, N, batch;
+    long long stride_c;
+    int m_tiles, n_tiles;
+    int k_steps;             // ceil(K / 32): MMAs beyond it would multiply the zero padding
+    int e0;
+};
+
+template <int S>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const SmallKParams P) {
+    using Tr = SmallKTraits<S>;
+    constexpr int NT = SK_NT, CPT = Tr::CPT;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = smem_base + 2 * Tr::A_BYTES;
+    const uint32_t bar_base = b_base + SK_B_STAGES * Tr::B_STAGE_BYTES;
+    auto a_full = [&](int i) { return bar_base + 8u * i; };
+    auto a_empty = [&](int i) { return bar_base + 8u * (2 + i); };
+    auto b_full = [&](int s) { return bar_base + 8u * (4 + s); };
+    auto b_empty = [&](int s) { return bar_base + 8u * (4 + SK_B_STAGES + s); };
+    auto tmem_full = [&](int g) { return bar_base + 8u * (4 + 2 * SK_B_STAGES + g); };
+    auto tmem_empty = [&](int g) { return bar_base + 8u * (6 + 2 * SK_B_STAGES + g); };
+    const uint32_t tmem_slot = bar_base + 8u * (8 + 2 * SK_B_STAGES);
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint8_t* gen_bar = gen_base + 2 * Tr::A_BYTES + SK_B_STAGES * Tr::B_STAGE_BYTES;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_bar + 8 * (8 + 2 * SK_B_STAGES));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_bar + 8 * (9 + 2 * SK_B_STAGES));
+    int* eb_slots = reinterpret_cast<int*>(gen_bar + Tr::BAR_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // this CTA's contiguous range of tiles; flat order: batch, row tile, column tile (fastest)
+    const long long total = (long long)P.batch * P.m_tiles * P.n_tiles;
+    const long long t0 = total * blockIdx.x / gridDim.x, t1 = total * (blockIdx.x + 1) / gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
+        for (int s = 0; s < SK_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+        for (int g = 0; g < SK_EPI_GROUPS; ++g) { mbar_init(tmem_full(g), 1); mbar_init(tmem_empty(g), SK_GROUP_THREADS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Tr::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t a_it = 0, b_it = 0;
+            long long prev_group = -1;
+            bool ok = true;
+            for (long long t = t0; t < t1; ++t, ++b_it) {
+                const long long group = t / P.n_tiles;
+                const int n_blk = (int)(t - group * P.n_tiles);
+                const int batch = (int)(group / P.m_tiles), m_blk = (int)(group - (long long)batch * P.m_tiles);
+                if (group != prev_group) {
+                    const int ab = a_it & 1;
+                    if (!(ok = mbar_wait(a_empty(ab), ((a_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
+                    mbar_arrive_expect_tx(a_full(ab), Tr::A_BYTES);
+                    tma_load_4d(a_base + ab * Tr::A_BYTES, &tmap_a, a_full(ab), 0, m_blk * BLOCK_M, 0, batch);
+                    ++a_it;
+                    prev_group = group;
+                }
+                const int s = b_it % SK_B_STAGES;
+                if (!(ok = mbar_wait(b_empty(s), ((b_it / SK_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
+                mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
+                tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), 0, n_blk * NT, 0, batch);
+            }
+            if (!ok) {
+                // abort: let copies that are still in flight land before the CTA gives up its shared memory
+                auto drain = [&](uint32_t bar, uint32_t parity) {
+                    long long c0 = clock64();
+                    while (!mbar_try_wait(bar, parity))
+                        if (clock64() - c0 > WAIT_LIMIT_CLOCKS) { atomicCAS(P.status, 0, STATUS_WAIT_DRAIN); break; }
+                };
+                for (uint32_t j = 0; j < (b_it < (uint32_t)SK_B_STAGES ? b_it : (uint32_t)SK_B_STAGES); ++j) {
+                    const uint32_t i2 = b_it - 1 - j;
+                    drain(b_full(i2 % SK_B_STAGES), (i2 / SK_B_STAGES) & 1u);
+                }
+                for (uint32_t j = 0; j < (a_it < 2u ? a_it : 2u); ++j) {
+                    const uint32_t i2 = a_it - 1 - j;
+                    drain(a_full(i2 & 1), (i2 >> 1) & 1u);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
+            constexpr uint32_t IDESC_ONE = idesc_i8(BLOCK_M, NT);
+            uint32_t a_it = 0, b_it = 0;
+            long long prev_group = -1;
+            uint32_t sa = 0, cur_ab = 0;
+            bool ok = true;
+            for (long long t = t0; ok && t < t1; ++t, ++b_it) {
+                const long long group = t / P.n_tiles;
+                if (group != prev_group) {
+                    cur_ab = a_it & 1;
+                    if (!(ok = mbar_wait(a_full(cur_ab), (a_it >> 1) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                    sa = a_base + cur_ab * Tr::A_BYTES;
+                    ++a_it;
+                    prev_group = group;
+                }
+                const int s = b_it % SK_B_STAGES;
+                if (!(ok = mbar_wait(b_full(s), (b_it / SK_B_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                const int g = b_it & 1;                 // accumulator set = tile parity
+                if (!(ok = mbar_wait(tmem_empty(g), ((b_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
+                tc_fence_after();
+                const uint32_t sb = b_base + s * Tr::B_STAGE_BYTES;
+                const uint32_t acc = tmem_base + g * Tr::ACC_COLS;
+                // first k step: every level block needs its own overwrite flag
+#pragma unroll
+                for (int p = 0; p < S; ++p)
+#pragma unroll
+                    for (int q = 0; q < S; ++q)
+                        umma_i8(acc + (p + q) * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES),
+                                smem_desc_sw128(sb + q * Tr::B_PLANE_BYTES), IDESC_ONE, (p != 0 && q != S - 1) ? 1u : 0u);
+                for (int k = 1; k < P.k_steps; ++k)
+#pragma unroll
+                    for (int p = 0; p < S; ++p)
+                        umma_i8(acc + p * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES + k * UMMA_K),
+                                smem_desc_sw128(sb + k * UMMA_K), IDESC_WIDE, 1u);
+                umma_commit(b_empty(s));
+                umma_commit(tmem_full(g));
+                // last tile of this row of tiles (or of the CTA's range): the A buffer may be refilled
+                if (t + 1 == t1 || (t + 1) / P.n_tiles != group) umma_commit(a_empty(cur_ab));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (two groups of eight warps)
+        using TAcc = typename std::conditional<S == 1, int, long long>::type;
+        const int ew = warp - 2;
+        const int g = ew / SK_GROUP_WARPS;             // accumulator set of this group
+        const int quarter = warp & 3;                  // TMEM lanes this warp may read
+        const int half = (ew % SK_GROUP_WARPS) >> 2;   // which half of the tile's columns
+        const int row_in_tile = quarter * 32 + lane;
+        int* eb_s = eb_slots + ew * CPT;
+        bool ok = true;
+        uint32_t use = 0;                              // how often this group's accumulator set has been used
+        for (long long t = t0 + g; ok && t < t1; t += SK_EPI_GROUPS, ++use) {
+            const long long group = t / P.n_tiles;
+            const int n_blk = (int)(t - group * P.n_tiles);
+            const int batch = (int)(group / P.m_tiles), m_blk = (int)(group - (long long)batch * P.m_tiles);
+            const int row = m_blk * BLOCK_M + row_in_tile;
+            const bool row_ok = row < P.M;
+            const int ea = row_ok ? __ldg(P.expo_a + (size_t)batch * P.M + row) : 0;
+            const int col0 = n_blk * NT + half * CPT;
+            __syncwarp();
+            if (lane < CPT) eb_s[lane] = col0 + lane < P.N ? __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane) : 0;
+            __syncwarp();
+            ok = mbar_wait(tmem_full(g), use & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            // accumulators -> exact sums in registers, then hand the set back to the MMA warp
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + g * Tr::ACC_COLS + half * CPT;
+            TAcc T[CPT];
+#pragma unroll
+            for (int c0 = 0; c0 < CPT; c0 += 8) {       // eight columns at a time keeps the register count low
+                int lv[Tr::LEVELS][8];
+#pragma unroll
+                for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    long long v = lv[Tr::LEVELS - 1][j];
+#pragma unroll
+                    for (int L = Tr::LEVELS - 2; L >= 0; --L)
+                        v += (long long)lv[L][j] * (long long)(1 << (7 * (Tr::LEVELS - 1 - L)));
+                    T[c0 + j] = (TAcc)v;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tmem_empty(g));
+            if (!row_ok || col0 >= P.N) continue;
+            // one rounding per output
+            uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
+            const int ebase = ea + P.e0;
+            auto round4 = [&](int j, uint32_t (&r)[4]) {
+                bool k0, k1, k2, k3;
+                r[0] = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
+                r[1] = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
+                r[2] = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
+                r[3] = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
+                    r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
+                    r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
+                    r[2] = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
+                    r[3] = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
+                }
+            };
+            const bool whole = col0 + CPT <= P.N;
+            if (whole && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+                for (int j = 0; j < CPT; j += 8) {
+                    uint32_t r[4], q[4];
+                    round4(j, r);
+                    round4(j + 4, q);
+                    st_global_256(dst + j, r[0], r[1], r[2], r[3], q[0], q[1], q[2], q[3]);
+                }
+            } else if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CPT; j += 4) {
+                    uint32_t r[4];
+                    round4(j, r);
+                    *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CPT; j += 4) {
+                    uint32_t r[4];
+                    round4(j, r);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (col0 + j + q < P.N) dst[j + q] = r[q];
+                }
+            }
+        }
+    }
+
+    // common exit: every thread arrives, then the allocating warp returns the TMEM columns
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Tr::TMEM_COLS);
+    }
+}
+
+}  // namespace rgb200

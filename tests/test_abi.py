@@ -193,6 +193,47 @@ def test_plan_without_a_device_fails_cleanly(L):
     assert rc == rg.cudaErrorNotSupported
 
 
+def test_host_pipeline_without_a_device_fails_cleanly(L):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    h = C.c_void_p()
+    c = rg.Config().c()
+    assert L.rgb200_host_gemm_create(256, 256, 256, C.byref(c), 0, C.byref(h)) != 0 and not h.value
+    assert L.rgb200_host_gemm_create(256, 256, 256, C.byref(c), 0, None) == rg.cudaErrorInvalidValue
+    assert L.rgb200_gemm_fp32_host(None, None, None, None, None) == rg.cudaErrorInvalidValue
+    assert L.rgb200_host_gemm_destroy(None) == rg.cudaErrorInvalidValue
+    assert L.rgb200_static_status(None) == rg.cudaErrorInvalidValue
+
+
+def test_device_generator_reproduces_the_numpy_streams():
+    """The torch generator (used to create large operands on a GPU) gives the numpy generator's bits."""
+    import torch
+
+    def same(a, b):
+        return np.array_equal(np.asarray(a).view(np.uint32), b.cpu().numpy().view(np.uint32))
+    n = 70001
+    g, d = fx.Rng(4), fx.DeviceRng(4, "cpu")
+    assert same(g.uniform_pm1(n), d.uniform_pm1(n)) and same(g.uniform_pm1(33), d.uniform_pm1(33))
+    g, d = fx.Rng(3), fx.DeviceRng(3, "cpu")
+    assert same(g.wide_mixed(n), d.wide_mixed(n)) and same(g.wide_mixed(n), d.wide_mixed(n))
+    g, d = fx.Rng(5), fx.DeviceRng(5, "cpu")
+    assert same(g.normal(n), d.normal(n)) and same(g.normal(n, 0.02), d.normal(n, 0.02))
+    assert same(g.prob_rows(37, 1024), d.prob_rows(37, 1024))
+    c = fx.config4(192)[0]
+    A, B = fx.config4_device("cpu", 192, a_rows=(64, 128))
+    assert same(c["A"].reshape(192, 192)[64:128].reshape(-1), A) and same(c["B"], B)
+    A, B = fx.config4_device_k_range("cpu", 192, 32, 96)
+    assert same(np.ascontiguousarray(c["A"].reshape(192, 192)[:, 32:96]).reshape(-1), A)
+    assert same(c["B"].reshape(192, 192)[32:96].reshape(-1), B)
+    c3 = fx.config3(64)[0]
+    A, B = fx.config3_device("cpu", 64)
+    assert same(c3["A"], A) and same(c3["B"], B)
+    c5 = fx.config5(2, 16, 64)
+    Q, Km, V, P = fx.config5_device("cpu", 2, 16, 64)
+    assert same(c5[0]["A"], Q) and same(c5[0]["B"], Km) and same(c5[1]["B"], V) and same(c5[1]["A"], P)
+
+
 CXX_CALLER = r"""
 // A caller written against the reference's C++ surface (repro_gemm_cuda/repro_gemm.cuh:25-75).
 #include "repro_gemm.cuh"

@@ -150,3 +150,14 @@ def test_properties_at_full_size():
     # transposed storage of either operand does not change a bit
     assert torch.equal(rg.gemm(A.t().contiguous(), B.t().contiguous(), n, n, n, True, True).view(torch.int32),
                        base.view(torch.int32))
+
+
+def test_device_generated_operands_have_the_golden_input_hashes(golden):
+    """The operands bench.py generates on the GPU carry the bits the golden outputs were computed from."""
+    A, B = fx.config3_device("cuda", 4096)
+    assert "%016x" % rg.fnv1a64(B, rg.fnv1a64(A)) == golden[("c3.4096", 3)]["in_hash"]
+    A, B = fx.config4_device("cuda", 2048)
+    assert "%016x" % rg.fnv1a64(B, rg.fnv1a64(A)) == golden[("c4.2048", 3)]["in_hash"]
+    Q, Km, V, P = fx.config5_device("cuda", 4)
+    assert "%016x" % rg.fnv1a64(Km, rg.fnv1a64(Q)) == golden[("c5.QKt.b4", 3)]["in_hash"]
+    assert "%016x" % rg.fnv1a64(V, rg.fnv1a64(P)) == golden[("c5.PV.b4", 3)]["in_hash"]
