@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <new>
 #include <vector>
@@ -268,6 +269,20 @@ cudaError_t encode_kstrided_map(CUtensorMap* map, const float* src, int R, int K
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// FP32 operand stored [batch][M][K] (k contiguous), as the fused-split kernel streams it: dims (k, row, batch),
+// box (64 k, 128 rows, 1), zero fill beyond K and M.
+cudaError_t encode_kmajor_f32_map(CUtensorMap* map, const float* src, int M, int K, int batch, long long batch_stride) {
+    if (!ensure_encode()) return cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)M * K) * 4};
+    cuuint32_t box[3] = {(cuuint32_t)RF_CHUNK_K, (cuuint32_t)BLOCK_M, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(src), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 // The cluster form of the k-strided split (one read of the operand).  Returns false when the operand cannot
 // take it (rows not a multiple of four floats, unaligned base or batch stride, K too long for a slab), and the
 // caller then runs the two-kernel form.
@@ -285,7 +300,13 @@ bool try_cluster_split(const float* src, const float* given_max, int8_t* planes,
     if (R % 4 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (batch > 1 && batch_stride % 4 != 0)) return false;
     if (!ensure_encode()) return false;
     const int KC = ceil_div(ceil_div(Kp, KSC_CLUSTER), KSC_BOX_K) * KSC_BOX_K;
-    int W = 32;
+    // panel width: RGB200_CLUSTER_PANEL (32, 16 or 8; a tuning knob read once) or the widest whose slab fits
+    static const int forced_w = [] {
+        const char* v = std::getenv("RGB200_CLUSTER_PANEL");
+        const int w = v ? std::atoi(v) : 0;
+        return (w == 32 || w == 16 || w == 8) ? w : 0;
+    }();
+    int W = forced_w ? forced_w : 32;
     while (W > 8 && (size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) W >>= 1;
     if ((size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) return false;
     while (W > 8 && (long long)ceil_div(R, W) * KSC_CLUSTER * batch < PLAN_SM_COUNT) W >>= 1;   // few columns: narrower panels, more CTAs
@@ -318,6 +339,13 @@ void launch_kmajor(const KmajorOperand& first, const KmajorOperand& second, int 
         split_kmajor_kernel<S, TPR, CH, VEC><<<dim3(b1 + b2, batch), PREPASS_THREADS, 0, st>>>(               \
             first, second, b1, K, Kp, zero_word);                                                             \
     } while (0)
+    if (aligned && Kp == 128) {                          // short rows: a small grid of warps, each walking over many rows
+        const long long rows = (long long)first.R + (two ? second.R : 0);
+        const long long want = (rows + 63) / 64;         // eight rows per warp at least
+        const int ctas = (int)(want < 1 ? 1 : (want > PLAN_SM_COUNT * 8 ? PLAN_SM_COUNT * 8 : want));
+        split_kmajor_short_kernel<S><<<dim3(ctas, batch), PREPASS_THREADS, 0, st>>>(first, second, K, zero_word);
+        return;
+    }
     if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS) {      // general path: any K, any alignment; row group sized to the row
         if (nq <= 64) RGB_KMAJOR(32, 1, false);
         else if (nq <= 256) RGB_KMAJOR(64, 1, false);
@@ -432,15 +460,16 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
             record(0);
         }
         record(1);
-        CUtensorMap map_b;
+        CUtensorMap map_a, map_b;
+        if ((e = encode_kmajor_f32_map(&map_a, a.A, L.M, L.K, L.batch, a.stride_a)) != cudaSuccess) return e;
         if ((e = encode_planes_map(&map_b, qb, L.N, L.Kp, S, L.batch, RF_NT)) != cudaSuccess) return e;
         RowFusedParams Q;
-        Q.A = a.A; Q.stride_a = a.stride_a; Q.expo_b = eb; Q.C = a.C; Q.status = status;
+        Q.expo_b = eb; Q.C = a.C; Q.status = status;
         Q.M = L.M; Q.N = L.N; Q.K = L.K; Q.batch = L.batch; Q.stride_c = a.stride_c;
         Q.m_tiles = ceil_div(L.M, BLOCK_M); Q.k_blocks = L.k_blocks; Q.e0 = e0;
         const long long rf_tiles = (long long)L.batch * Q.m_tiles;
         const int rf_grid = (int)(rf_tiles < dev.sm_count ? rf_tiles : dev.sm_count);
-        gemm_i8_rowfused_kernel<S><<<rf_grid, RF_THREADS, RowFusedTraits<S>::SMEM_BYTES, a.st>>>(map_b, Q);
+        gemm_i8_rowfused_kernel<S><<<rf_grid, RF_THREADS, RowFusedTraits<S>::SMEM_BYTES, a.st>>>(map_a, map_b, Q);
         record(2);
         record(3);
         return cudaGetLastError();

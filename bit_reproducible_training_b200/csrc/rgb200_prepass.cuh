@@ -185,6 +185,57 @@ split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int b
     }
 }
 
+// Short rows (K <= 128, one padded k block per row; 16-byte aligned rows): a warp per row, and every warp walks
+// over many rows so that the grid stays small - with one row per warp the launch of tens of thousands of tiny
+// CTAs costs more than the rows' traffic.  Two rows are in flight per warp.  Same two-operand convention as
+// split_kmajor_kernel.  grid = (CTAs, batch); any CTA count works.
+template <int S>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+split_kmajor_short_kernel(const KmajorOperand first, const KmajorOperand second, int K, int* zero_word) {
+    constexpr int KP = 128;
+    if (zero_word && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *zero_word = 0;
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.y;
+    const int nq = K >> 2;
+    const int rows_total = first.R + second.R;
+    const int warps_total = gridDim.x * (PREPASS_THREADS / 32);
+    // the operand's fields are picked one by one (a pointer to a kernel parameter would force it into local memory)
+    struct RowRef { const float* src; const float* given_max; int8_t* planes; int* expo; int R; int r; };
+    auto locate = [&](int row) {
+        const bool f = row < first.R;
+        RowRef x;
+        x.R = f ? first.R : second.R;
+        x.r = f ? row : row - first.R;
+        x.src = (f ? first.src : second.src) + (size_t)b * (f ? first.batch_stride : second.batch_stride) + (size_t)x.r * K;
+        x.given_max = f ? first.given_max : second.given_max;
+        x.planes = f ? first.planes : second.planes;
+        x.expo = f ? first.expo : second.expo;
+        return x;
+    };
+    auto load = [&](const RowRef& x) {
+        return lane < nq ? __ldg(reinterpret_cast<const float4*>(x.src) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto finish = [&](const RowRef& x, float4 v) {
+        float m = abs4max(0.0f, v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        if (x.given_max) m = x.given_max[(size_t)b * x.R + x.r];
+        const int e = scale_exponent(m);
+        if (lane == 0) x.expo[(size_t)b * x.R + x.r] = e;
+        const size_t plane_stride = (size_t)x.R * KP;
+        store_quad<S>(v, quant_scale(e, S), plain_row(e), x.planes + (size_t)b * S * plane_stride + (size_t)x.r * KP, plane_stride,
+                      (size_t)lane * 4);
+    };
+    for (int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5); row < rows_total; row += 2 * warps_total) {
+        const bool two = row + warps_total < rows_total;
+        const RowRef x0 = locate(row), x1 = locate(two ? row + warps_total : row);
+        const float4 v0 = load(x0);
+        const float4 v1 = two ? load(x1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        finish(x0, v0);
+        if (two) finish(x1, v1);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // k-strided operand: element (r, k) at src[k*R + r]   (B without trans_b, A with trans_a).
 // Pass 1: column maxima over K with an integer atomicMax (|x| >= 0 orders like its bit pattern,

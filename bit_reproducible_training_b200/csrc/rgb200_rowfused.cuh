@@ -5,32 +5,38 @@
 // For such a product A is nearly all of the traffic: staging its S digit planes in HBM, as the general
 // path does, writes and re-reads S bytes per element on top of the four that must be read.  Here a CTA
 // owns a 128-row block of A and never stores its planes:
-//   pass 1  sixteen warps stream the block's rows (16-byte loads, a warp per 512-byte row segment) and
-//           keep a running maximum per row; the row's scale exponent follows;
-//   pass 2  the same warps read the rows again (the block was just read, so most of it comes from L2),
-//           round to the fixed-point integer, split it into S digits and store them straight into the
-//           128-byte-swizzled shared-memory image the MMA reads - the layout TMA would have produced -
-//           one k block (128 values per row) per pipeline stage;
-//   MMA     one thread issues the same level-accumulating MMAs as the general kernel, against B's digit
-//           planes, which are small and still come from HBM/L2 by TMA;
+//   producer one thread streams the block's rows through a ring of shared-memory stages with TMA, as FP32
+//           chunks of 128 rows x 64 k (zero-filled beyond M and K), twice: once for pass 1, once for pass 2
+//           (the block was just read, so the second time most of it comes from L2), and, during pass 2, B's
+//           digit planes (small, staged in HBM by the usual pre-pass) one k block at a time;
+//   pass 1  sixteen warps take the row maxima of the chunks as they land; the rows' scale exponents follow;
+//   pass 2  the same warps round every value to its fixed-point integer, split it into S digits and store
+//           them straight into the 128-byte-swizzled shared-memory image the MMA reads - the layout TMA
+//           would have produced - one k block (two chunks) per MMA stage;
+//   MMA     one thread issues the same level-accumulating MMAs as the general kernel;
 //   finish  the sixteen warps drain TMEM, rebuild the exact sums, round once and store C.
+// Because the copies are asynchronous the chunks of pass 1, pass 2 and of the next tile follow each other
+// without the warps ever waiting for a load they issued themselves.
 // The arithmetic is that of the general kernel (rgb200_mma.cuh) and of the split pre-pass
 // (rgb200_prepass.cuh); only where the digits of A live differs.  Reference counterparts:
 // quantize_kmajor + gemm_wmma_i8 (repro_gemm_cuda/repro_gemm.cu:54-79, 280-364).
 #pragma once
 #include "rgb200_mma.cuh"
 #include "rgb200_prepass.cuh"
+#include "rgb200_prepass_cluster.cuh"
 #include "rgb200_smallk.cuh"
 
 namespace rgb200 {
 
 constexpr int RF_NT = 64;                     // columns of C per tile (one tile covers all of N)
-constexpr int RF_A_STAGES = 3;
-constexpr int RF_B_STAGES = 3;
+constexpr int RF_A_STAGES = 2;                // int8 stages the MMA reads (one k block each)
+constexpr int RF_B_STAGES = 2;
+constexpr int RF_F_STAGES = 2;                // FP32 landing stages
+constexpr int RF_CHUNK_K = 64;                // k per FP32 chunk
+constexpr int RF_F_STAGE_BYTES = BLOCK_M * RF_CHUNK_K * 4;
 constexpr int RF_WORK_WARPS = 16;             // converter + epilogue warps
 constexpr int RF_WORK_THREADS = RF_WORK_WARPS * 32;
 constexpr int RF_THREADS = 64 + RF_WORK_THREADS;      // 576
-constexpr int RF_ROWS_PER_WARP = BLOCK_M / RF_WORK_WARPS;   // 8
 
 template <int S>
 struct RowFusedTraits {
@@ -43,14 +49,12 @@ struct RowFusedTraits {
     static constexpr int TMEM_COLS = ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     static constexpr int CPT = RF_NT / 4;     // sixteen columns per epilogue thread
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = RF_A_STAGES * A_STAGE_BYTES + RF_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
+    static constexpr int SMEM_BYTES = RF_F_STAGES * RF_F_STAGE_BYTES + RF_A_STAGES * A_STAGE_BYTES + RF_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
                                       RF_WORK_WARPS * CPT * 4 /* column exponents */ + BLOCK_M * 4 /* row exponents */;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 struct RowFusedParams {
-    const float* A;          // [batch][M][K], k contiguous
-    long long stride_a;      // elements between batches
     const int* expo_b;       // [batch][N]
     float* C;
     int* status;
@@ -62,19 +66,23 @@ struct RowFusedParams {
 
 template <int S>
 __global__ void __launch_bounds__(RF_THREADS, 1)
-gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFusedParams P) {
+gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const RowFusedParams P) {
     using Tr = RowFusedTraits<S>;
     constexpr int NT = RF_NT, CPT = Tr::CPT;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = smem_base + RF_A_STAGES * Tr::A_STAGE_BYTES;
-    const uint32_t bar_base = b_base + RF_B_STAGES * Tr::B_STAGE_BYTES;
+    const uint32_t f_base = b_base + RF_B_STAGES * Tr::B_STAGE_BYTES;
+    const uint32_t bar_base = f_base + RF_F_STAGES * RF_F_STAGE_BYTES;
     auto a_full = [&](int s) { return bar_base + 8u * s; };
     auto a_empty = [&](int s) { return bar_base + 8u * (RF_A_STAGES + s); };
     auto b_full = [&](int s) { return bar_base + 8u * (2 * RF_A_STAGES + s); };
     auto b_empty = [&](int s) { return bar_base + 8u * (2 * RF_A_STAGES + RF_B_STAGES + s); };
-    constexpr int NBAR = 2 * RF_A_STAGES + 2 * RF_B_STAGES;
+    auto f_full = [&](int s) { return bar_base + 8u * (2 * RF_A_STAGES + 2 * RF_B_STAGES + s); };
+    auto f_empty = [&](int s) { return bar_base + 8u * (2 * RF_A_STAGES + 2 * RF_B_STAGES + RF_F_STAGES + s); };
+    constexpr int NBAR = 2 * RF_A_STAGES + 2 * RF_B_STAGES + 2 * RF_F_STAGES;
     const uint32_t tmem_full_bar = bar_base + 8u * NBAR;
     const uint32_t tmem_empty_bar = bar_base + 8u * (NBAR + 1);
     // two barriers among the sixteen work warps (one arrival per warp); waits on them are bounded like all others
@@ -83,7 +91,8 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFus
     const uint32_t tmem_slot = bar_base + 8u * (NBAR + 4);
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
     uint8_t* gen_a = gen_base;
-    uint8_t* gen_bar = gen_base + RF_A_STAGES * Tr::A_STAGE_BYTES + RF_B_STAGES * Tr::B_STAGE_BYTES;
+    const uint8_t* gen_f = gen_base + RF_A_STAGES * Tr::A_STAGE_BYTES + RF_B_STAGES * Tr::B_STAGE_BYTES;
+    uint8_t* gen_bar = gen_base + RF_A_STAGES * Tr::A_STAGE_BYTES + RF_B_STAGES * Tr::B_STAGE_BYTES + RF_F_STAGES * RF_F_STAGE_BYTES;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_bar + 8 * (NBAR + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_bar + 8 * (NBAR + 5));
     int* eb_slots = reinterpret_cast<int*>(gen_bar + Tr::BAR_BYTES);
@@ -95,6 +104,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFus
     if (threadIdx.x == 0) {
         for (int s = 0; s < RF_A_STAGES; ++s) { mbar_init(a_full(s), RF_WORK_WARPS); mbar_init(a_empty(s), 1); }
         for (int s = 0; s < RF_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+        for (int s = 0; s < RF_F_STAGES; ++s) { mbar_init(f_full(s), 1); mbar_init(f_empty(s), RF_WORK_WARPS); }
         mbar_init(tmem_full_bar, 1);
         mbar_init(tmem_empty_bar, RF_WORK_THREADS);
         mbar_init(rows_bar, RF_WORK_WARPS);
@@ -110,25 +120,44 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFus
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer (B planes only)
+        // ---------------------------------------------------------------- TMA producer (FP32 chunks of A, planes of B)
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t f_it = 0, b_it = 0;
             bool ok = true;
+            auto load_chunk = [&](int c, int m_blk, int batch) {
+                const int s = f_it % RF_F_STAGES;
+                if (!mbar_wait(f_empty(s), ((f_it / RF_F_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY)) return false;
+                mbar_arrive_expect_tx(f_full(s), RF_F_STAGE_BYTES);
+                tma_load_3d(f_base + s * RF_F_STAGE_BYTES, &tmap_a, f_full(s), c * RF_CHUNK_K, m_blk * BLOCK_M, batch);
+                ++f_it;
+                return true;
+            };
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int batch = tile / P.m_tiles;
-                for (int kb = 0; kb < P.k_blocks; ++kb, ++it) {
-                    const int s = it % RF_B_STAGES;
-                    if (!(ok = mbar_wait(b_empty(s), ((it / RF_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
+                const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
+                for (int c = 0; ok && c < 2 * P.k_blocks; ++c) ok = load_chunk(c, m_blk, batch);          // pass 1
+                for (int kb = 0; ok && kb < P.k_blocks; ++kb) {                                            // pass 2
+                    const int s = b_it % RF_B_STAGES;
+                    if (!(ok = mbar_wait(b_empty(s), ((b_it / RF_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                     mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
                     tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), kb * BLOCK_K, 0, 0, batch);
+                    ++b_it;
+                    ok = load_chunk(2 * kb, m_blk, batch) && load_chunk(2 * kb + 1, m_blk, batch);
                 }
             }
             if (!ok) {
-                for (uint32_t j = 0; j < (it < (uint32_t)RF_B_STAGES ? it : (uint32_t)RF_B_STAGES); ++j) {
-                    const uint32_t i2 = it - 1 - j;
+                // abort: let copies that are still in flight land before the CTA gives up its shared memory
+                auto drain = [&](uint32_t bar, uint32_t parity) {
                     long long c0 = clock64();
-                    while (!mbar_try_wait(b_full(i2 % RF_B_STAGES), (i2 / RF_B_STAGES) & 1u))
+                    while (!mbar_try_wait(bar, parity))
                         if (clock64() - c0 > WAIT_LIMIT_CLOCKS) { atomicCAS(P.status, 0, STATUS_WAIT_DRAIN); break; }
+                };
+                for (uint32_t j = 0; j < (b_it < (uint32_t)RF_B_STAGES ? b_it : (uint32_t)RF_B_STAGES); ++j) {
+                    const uint32_t i2 = b_it - 1 - j;
+                    drain(b_full(i2 % RF_B_STAGES), (i2 / RF_B_STAGES) & 1u);
+                }
+                for (uint32_t j = 0; j < (f_it < (uint32_t)RF_F_STAGES ? f_it : (uint32_t)RF_F_STAGES); ++j) {
+                    const uint32_t i2 = f_it - 1 - j;
+                    drain(f_full(i2 % RF_F_STAGES), (i2 / RF_F_STAGES) & 1u);
                 }
             }
         }
@@ -174,76 +203,83 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFus
     } else {
         // ---------------------------------------------------------------- converters, then epilogue (warps 2..17)
         using TAcc = typename std::conditional<S == 1, int, long long>::type;
-        constexpr int RPW = RF_ROWS_PER_WARP;
         const int cw = warp - 2;
         const int quarter = warp & 3;                  // TMEM lanes this warp may read
         const int cgroup = cw >> 2;                    // which sixteen columns of the tile
         int* eb_s = eb_slots + cw * CPT;
-        const int k_chunks = P.K >> 2;                 // float4 chunks per row (K % 4 == 0 is a launch condition)
-        uint32_t it = 0, tile_it = 0;
+        // Chunk layout in shared memory: [128 rows][64 k] FP32, 256 bytes per row.  A warp owns eight rows; one
+        // 16-byte load per lane covers two rows at a time (16 lanes each), rows i and i + 4 of the eight, so that
+        // the swizzled digit stores of the two half-warps fall into different bank groups.
+        const int c16 = lane & 15;                     // which four k of the chunk's 64
+        const int rsel = lane >> 4;
+        uint32_t f_it = 0, a_it = 0, tile_it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
             const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
-            const int row0 = m_blk * BLOCK_M + cw * RPW;                       // this warp's first row
-            const float4* src = reinterpret_cast<const float4*>(P.A + (size_t)batch * P.stride_a + (size_t)row0 * P.K);
             // pass 1: row maxima
-            float m[RPW];
+            float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int c = 0; c < 2 * P.k_blocks; ++c, ++f_it) {
+                const int s = f_it % RF_F_STAGES;
+                ok = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
 #pragma unroll
-            for (int i = 0; i < RPW; ++i) m[i] = 0.0f;
-            for (int kb = 0; kb < P.k_blocks; ++kb) {
-                const int c = kb * 32 + lane;
-                float4 v[RPW];
-#pragma unroll
-                for (int i = 0; i < RPW; ++i)
-                    v[i] = (row0 + i < P.M && c < k_chunks) ? __ldg(src + (size_t)i * k_chunks + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int i = 0; i < RPW; ++i) m[i] = abs4max(m[i], v[i]);
+                for (int i = 0; i < 4; ++i) {
+                    const int r = cw * 8 + i + 4 * rsel;
+                    m[i] = abs4max(m[i], *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + c16 * 16));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(f_empty(s));
             }
-            int e[RPW];
-            float f1[RPW];
+            if (!ok) break;
+            int e[4];
+            float f1[4];
             bool all_plain = true;
 #pragma unroll
-            for (int i = 0; i < RPW; ++i) {
+            for (int i = 0; i < 4; ++i) {
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) m[i] = fmaxf(m[i], __shfl_xor_sync(0xFFFFFFFFu, m[i], o));
+                for (int o = 8; o > 0; o >>= 1) m[i] = fmaxf(m[i], __shfl_xor_sync(0xFFFFFFFFu, m[i], o));   // over the row's 16 lanes
                 e[i] = scale_exponent(m[i]);
                 f1[i] = quant_scale(e[i], S).f1;
                 all_plain = all_plain && plain_row(e[i]);
+                if (c16 == 0) ea_rows[cw * 8 + i + 4 * rsel] = e[i];    // the previous tile's epilogue has finished reading (done_bar)
             }
-            // the previous tile's epilogue has finished reading ea_rows (it ends with the barrier below)
-            if (lane < RPW) {
-                int ev = e[0];
-#pragma unroll
-                for (int i = 1; i < RPW; ++i) ev = lane == i ? e[i] : ev;
-                ea_rows[cw * RPW + lane] = ev;
-            }
+            all_plain = __all_sync(0xFFFFFFFFu, all_plain);
             // pass 2: digits into the swizzled stages
-            for (int kb = 0; kb < P.k_blocks; ++kb, ++it) {
-                const int c = kb * 32 + lane;
-                float4 v[RPW];
-#pragma unroll
-                for (int i = 0; i < RPW; ++i)
-                    v[i] = (row0 + i < P.M && c < k_chunks) ? __ldg(src + (size_t)i * k_chunks + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                const int s = it % RF_A_STAGES;
-                ok = mbar_wait(a_empty(s), ((it / RF_A_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY);
+            for (int kb = 0; kb < P.k_blocks; ++kb, ++a_it) {
+                const int sa_i = a_it % RF_A_STAGES;
+                ok = mbar_wait(a_empty(sa_i), ((a_it / RF_A_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                uint8_t* stage = gen_a + s * Tr::A_STAGE_BYTES;
+                uint8_t* stage = gen_a + sa_i * Tr::A_STAGE_BYTES;
 #pragma unroll
-                for (int i = 0; i < RPW; ++i) {
-                    const int r = cw * RPW + i;                                 // row inside the tile
-                    // 128-byte rows, 16-byte chunks XOR-ed with the row index modulo 8: the 128-byte swizzle
-                    const size_t off = (size_t)r * 128 + ((((lane >> 2) ^ (r & 7))) << 4) + ((lane & 3) << 2);
-                    if (all_plain) {
-                        QuantScale q; q.f1 = f1[i]; q.f2 = 1.0f; q.lim = 0;
-                        store_quad_impl<S, true>(v[i], q, reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
-                    } else {
-                        store_quad<S>(v[i], quant_scale(e[i], S), plain_row(e[i]), reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
+                for (int h = 0; h < 2; ++h, ++f_it) {
+                    const int s = f_it % RF_F_STAGES;
+                    ok = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
+                    if (!ok) break;
+                    const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = cw * 8 + i + 4 * rsel;                      // row inside the tile
+                        const float4 v = *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + c16 * 16);
+                        // 128-byte rows of int8, 16-byte chunks XOR-ed with the row index modulo 8: the 128-byte swizzle
+                        const size_t off = (size_t)r * 128 + (size_t)((((4 * h + (c16 >> 2)) ^ (r & 7))) << 4) + ((c16 & 3) << 2);
+                        if (all_plain) {
+                            QuantScale q; q.f1 = f1[i]; q.f2 = 1.0f; q.lim = 0;
+                            store_quad_impl<S, true>(v, q, reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
+                        } else {
+                            store_quad<S>(v, quant_scale(e[i], S), plain_row(e[i]), reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
+                        }
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(f_empty(s));
                 }
+                if (!ok) break;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> visible to the MMA's reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(a_full(s));
+                if (lane == 0) mbar_arrive(a_full(sa_i));
             }
             if (!ok) break;
             // every warp's row exponents are in ea_rows before any warp's epilogue reads them
@@ -291,10 +327,10 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_b, const RowFus
                 for (int j = 0; j < CPT; j += 4) {
                     uint32_t r[4];
                     bool k0, k1, k2, k3;
-                    r[0] = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
-                    r[1] = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
-                    r[2] = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
-                    r[3] = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                    r[0] = round_to_f32_bits_signed(T[j + 0], ebase + eb_s[j + 0], &k0);
+                    r[1] = round_to_f32_bits_signed(T[j + 1], ebase + eb_s[j + 1], &k1);
+                    r[2] = round_to_f32_bits_signed(T[j + 2], ebase + eb_s[j + 2], &k2);
+                    r[3] = round_to_f32_bits_signed(T[j + 3], ebase + eb_s[j + 3], &k3);
                     if (!(k0 && k1 && k2 && k3)) {
                         r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
                         r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);

@@ -34,6 +34,23 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
                  : "r"(taddr) : "memory");
 }
 
+// Exact sum T = sum_L level_L * 128^(2S-2-L) for level sums over at most 128 values of k.  Each level is then
+// below 128 * 20352 < 2^22, so neighbouring levels combine in 32-bit arithmetic (level * 128 stays below 2^29)
+// and only the last steps need 64 bits.
+template <int S>
+__device__ __forceinline__ typename std::conditional<S == 1, int, long long>::type
+combine_levels_short_k(const int (&lv)[2 * S - 1][8], int j) {
+    if constexpr (S == 1) {
+        return lv[0][j];
+    } else if constexpr (S == 2) {
+        return (long long)(lv[2][j] + lv[1][j] * 128) + (long long)lv[0][j] * 16384;
+    } else {
+        const int low = lv[4][j] + lv[3][j] * 128;
+        const int mid = lv[2][j] + lv[1][j] * 128;
+        return (long long)low + (long long)mid * 16384 + (long long)lv[0][j] * 268435456ll;
+    }
+}
+
 template <int S>
 struct SmallKTraits {
     static constexpr int LEVELS = 2 * S - 1;
@@ -225,13 +242,7 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    long long v = lv[Tr::LEVELS - 1][j];
-#pragma unroll
-                    for (int L = Tr::LEVELS - 2; L >= 0; --L)
-                        v += (long long)lv[L][j] * (long long)(1 << (7 * (Tr::LEVELS - 1 - L)));
-                    T[c0 + j] = (TAcc)v;
-                }
+                for (int j = 0; j < 8; ++j) T[c0 + j] = combine_levels_short_k<S>(lv, j);
             }
             tc_fence_before();
             mbar_arrive(tmem_empty(g));
@@ -241,10 +252,10 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const int ebase = ea + P.e0;
             auto round4 = [&](int j, uint32_t (&r)[4]) {
                 bool k0, k1, k2, k3;
-                r[0] = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
-                r[1] = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
-                r[2] = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
-                r[3] = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                r[0] = round_to_f32_bits_signed(T[j + 0], ebase + eb_s[j + 0], &k0);
+                r[1] = round_to_f32_bits_signed(T[j + 1], ebase + eb_s[j + 1], &k1);
+                r[2] = round_to_f32_bits_signed(T[j + 2], ebase + eb_s[j + 2], &k2);
+                r[3] = round_to_f32_bits_signed(T[j + 3], ebase + eb_s[j + 3], &k3);
                 if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
                     r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
                     r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);

@@ -46,6 +46,10 @@ def build(force=False):
         subprocess.run(["make", "-C", _HERE, "ref", ref_arg], check=True, capture_output=True)
     if force or not os.path.exists(_REF_CUDA) or not os.path.exists(REF_CONV_TEST_TOOL):
         subprocess.run(["make", "-C", _HERE, "ref_gpu", ref_arg], check=True, capture_output=True)
+    # the reference's torch extension with its GEMM and convolution kernels replaced by librgb200.so
+    from . import build_ref_torch
+    if force or build_ref_torch.built_module() is None:
+        build_ref_torch.build(root)
 
 
 def _f32(a):

@@ -76,3 +76,23 @@ def test_same_bits_as_the_reference_cuda_kernel_at_full_size():
         mine = rg.gemm(dA, dB, 4096, 4096, 4096, slices=S)
         theirs = oracle.ref_cuda_gemm(dA, dB, 4096, 4096, 4096, S=S)
         assert torch.equal(mine.view(torch.int32), theirs.view(torch.int32)), S
+
+
+def test_per_gpu_hash_files_from_separate_processes(tmp_path, golden):
+    """run_repro.sh's outer loop (repro_gemm_cuda/run_repro.sh:77-115) on this library: the reference's hash tool in
+    three separate processes per case on every visible GPU; one hash file per GPU; all processes and all GPUs agree,
+    and the hashes are the reference CPU implementation's."""
+    from oracle import run_repro_hashes as rr
+    if not os.path.exists(rr.TOOL):
+        pytest.skip("oracle/_ref/hash_repro_gemm_rgb200 not built")
+    gpus = [str(i) for i in range(torch.cuda.device_count())]
+    files, failures = rr.run(str(tmp_path), procs=3, gpus=gpus, slices=("1", "3"), shapes=rr.SHAPES[1:3],
+                             dists=("normal", "stress"))
+    assert not failures, failures
+    assert len(files) == len(gpus)
+    lines = open(files[0]).read().splitlines()
+    assert len(lines) == 2 * 2 * 2 and all("status=PASS" in l for l in lines)
+    for l in lines:
+        f = dict(kv.split("=") for kv in l.split()[1:])
+        want = golden[("hash.%s.%sx%sx%s" % (f["dist"], f["M"], f["N"], f["K"]), int(f["S"]))]["out_hash"]
+        assert f["hash"] == want

@@ -139,3 +139,17 @@ def test_attention_shapes_full_batch_by_golden_hash(golden):
     for name, A, B, M, N, K, tb in (("c5.QKt.b96", Q, Km, 1024, 1024, 64, True), ("c5.PV.b96", P, V, 1024, 64, 1024, False)):
         out = rg.gemm_batched(A, B, 96, M, N, K, False, tb, 3)
         assert "%016x" % rg.fnv1a64(out) == golden[(name, 3)]["out_hash"], name
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 30000), (256, 320, 20000), (512, 512, 12000), (300, 1000, 50000), (128, 36, 200),
+                                   (72, 4100, 640)])
+def test_single_read_split_of_k_strided_operands(shape):
+    """The cluster form of the k-strided split at every panel width (32, 16 and 8 columns), at the longest K a slab
+    holds and just beyond it (two-kernel form), for B and for a transposed A, with ragged last panels."""
+    M, N, K = shape
+    g = fx.Rng(4000 + M + N + K)
+    A, B = g.wide(M * K, -6, 6), g.wide_mixed(K * N)
+    for S in (1, 3):
+        want = oracle.gemm(A, B, M, N, K, S=S)
+        check(run(A, B, M, N, K, False, False, S), want, "%s S=%d" % (shape, S))
+        check(run(transposed(A, M, K), B, M, N, K, True, False, S), want, "%s S=%d ta" % (shape, S))
