@@ -445,6 +445,20 @@ def ksplit_records(args, world, rank, dA, dB, dC, cfg, flush, rows_ms):
                              "K ranges; maxima all-reduce, MMA epilogue stores INT64 tiles into the row owners over NVLink, one rounding per owner, FP32 all-gather")}
         del ks
         torch.cuda.empty_cache()
+    # the fused form leaving C sharded by rows (no FP32 all-gather): each rank's rows must equal the rows of the
+    # gathered result just verified
+    ks = sharded.KSplitState(M, N, K, world, cfg, dA, dB, fused=True, gather=False)
+    C_own = torch.full((own, N), float("nan"), dtype=torch.float32, device="cuda")
+    total_ms, _ = timed_loop(lambda: ks.step(C_own), steps, 3, flush, world)
+    ms = total_ms / steps
+    same = _all_ranks_true(torch.equal(C_own.view(-1).view(torch.int32), dC[rank * own * N:(rank + 1) * own * N].view(torch.int32)), world)
+    out["ksplit_fused"]["row_sharded_output"] = {
+        "ms_per_step": ms, "value": 2.0 * M * N * K * world / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "efficiency_vs_rows": rows_ms / ms, "matches_golden": bool(same and out["ksplit_fused"]["matches_golden"]),
+        "comm_bytes_per_rank": (world - 1) * own * N * 8 + (M + N) * 4,
+        "what": "as ksplit_fused, but every rank keeps only its M/N rows of C (no FP32 all-gather)"}
+    del ks
+    torch.cuda.empty_cache()
     return out
 
 

@@ -19,7 +19,7 @@
 #include "rgb200_smallk.cuh"
 #include "rgb200_rowfused.cuh"
 #include "rgb200_prepass.cuh"
-#include "rgb200_prepass_cluster.cuh"
+#include "rgb200_prepass_stream.cuh"
 #include "rgb200_conv.cuh"
 
 namespace rgb200 {
@@ -154,15 +154,6 @@ cudaError_t set_kernel_attrs() {
                                 GemmTraits<S, NT>::SMEM_BYTES);
 }
 
-template <int S>
-cudaError_t set_cluster_split_attrs() {
-    const int bytes = KSC_MAX_SLAB_BYTES + 128;
-    cudaError_t e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    return e;
-}
-
 cudaError_t device_info(const DeviceInfo** out) {
     int dev;
     cudaError_t e = cudaGetDevice(&dev);
@@ -196,11 +187,6 @@ cudaError_t device_info(const DeviceInfo** out) {
             if ((e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<1>::SMEM_BYTES)) != cudaSuccess ||
                 (e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<2>::SMEM_BYTES)) != cudaSuccess ||
                 (e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<3>::SMEM_BYTES)) != cudaSuccess) {
-                d.err = e2;
-                return;
-            }
-            if ((e2 = set_cluster_split_attrs<1>()) != cudaSuccess || (e2 = set_cluster_split_attrs<2>()) != cudaSuccess ||
-                (e2 = set_cluster_split_attrs<3>()) != cudaSuccess) {
                 d.err = e2;
                 return;
             }
@@ -256,19 +242,6 @@ cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, in
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-// FP32 operand stored [batch][K][R] (r contiguous), as the cluster split reads it: dims (r, k, batch), box (W, 64, 1).
-cudaError_t encode_kstrided_map(CUtensorMap* map, const float* src, int R, int K, int batch, long long batch_stride, int W) {
-    if (!ensure_encode()) return cudaErrorNotSupported;
-    cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)K, (cuuint64_t)batch};
-    cuuint64_t strides[2] = {(cuuint64_t)R * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)R * K) * 4};
-    cuuint32_t box[3] = {(cuuint32_t)W, (cuuint32_t)KSC_BOX_K, 1u};
-    cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(src), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
-}
-
 // FP32 operand stored [batch][M][K] (k contiguous), as the fused-split kernel streams it: dims (k, row, batch),
 // box (64 k, 128 rows, 1), zero fill beyond K and M.
 cudaError_t encode_kmajor_f32_map(CUtensorMap* map, const float* src, int M, int K, int batch, long long batch_stride) {
@@ -283,38 +256,17 @@ cudaError_t encode_kmajor_f32_map(CUtensorMap* map, const float* src, int M, int
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-// The cluster form of the k-strided split (one read of the operand).  Returns false when the operand cannot
-// take it (rows not a multiple of four floats, unaligned base or batch stride, K too long for a slab), and the
-// caller then runs the two-kernel form.
-template <int S, int W>
-void launch_cluster_split(const CUtensorMap& map, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp,
-                          int KC, int batch, int* status, cudaStream_t st) {
-    const size_t smem = (size_t)KC * W * 4 + 128;
-    split_kstrided_cluster_kernel<S, W><<<dim3(KSC_CLUSTER * ceil_div(R, W), batch), PREPASS_THREADS, smem, st>>>(
-        map, given_max, planes, expo, R, K, Kp, KC, status);
-}
-
+// The one-kernel form of the k-strided split (rgb200_prepass_stream.cuh): a cluster of eight CTAs per 32 columns.
+// Used when there are enough columns to fill the GPU that way; operands with few columns and a long K keep the
+// two-kernel form, which also spreads the work over k.
 template <int S>
-bool try_cluster_split(const float* src, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp, int batch,
-                       long long batch_stride, int* status, cudaStream_t st) {
-    if (R % 4 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (batch > 1 && batch_stride % 4 != 0)) return false;
-    if (!ensure_encode()) return false;
-    const int KC = ceil_div(ceil_div(Kp, KSC_CLUSTER), KSC_BOX_K) * KSC_BOX_K;
-    // panel width: RGB200_CLUSTER_PANEL (32, 16 or 8; a tuning knob read once) or the widest whose slab fits
-    static const int forced_w = [] {
-        const char* v = std::getenv("RGB200_CLUSTER_PANEL");
-        const int w = v ? std::atoi(v) : 0;
-        return (w == 32 || w == 16 || w == 8) ? w : 0;
-    }();
-    int W = forced_w ? forced_w : 32;
-    while (W > 8 && (size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) W >>= 1;
-    if ((size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) return false;
-    while (W > 8 && (long long)ceil_div(R, W) * KSC_CLUSTER * batch < PLAN_SM_COUNT) W >>= 1;   // few columns: narrower panels, more CTAs
-    CUtensorMap map;
-    if (encode_kstrided_map(&map, src, R, K, batch, batch_stride, W) != cudaSuccess) return false;
-    if (W == 32) launch_cluster_split<S, 32>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, st);
-    else if (W == 16) launch_cluster_split<S, 16>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, st);
-    else launch_cluster_split<S, 8>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, st);
+bool try_stream_split(const float* src, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp, int batch,
+                      long long batch_stride, cudaStream_t st) {
+    const long long ctas = (long long)ceil_div(R, KSS_W) * KSS_CLUSTER * batch;
+    if (ctas < 64) return false;
+    const int KC = ceil_div(ceil_div(Kp, KSS_CLUSTER), 32) * 32;
+    split_kstrided_stream_kernel<S><<<dim3(KSS_CLUSTER * ceil_div(R, KSS_W), batch), PREPASS_THREADS, 0, st>>>(
+        src, given_max, planes, expo, R, K, Kp, KC, batch_stride);
     return true;
 }
 
@@ -370,8 +322,8 @@ void launch_split(const float* src, bool k_major, const float* given_max, uint32
         const KmajorOperand op{src, given_max, planes, expo, R, batch_stride};
         const KmajorOperand none{nullptr, nullptr, nullptr, nullptr, 0, 0};
         launch_kmajor<S>(op, none, K, Kp, batch, nullptr, st);
-    } else if (try_cluster_split<S>(src, given_max, planes, expo, R, K, Kp, batch, batch_stride, status, st)) {
-        // one read of the operand; the zeroed maxima words stay unused
+    } else if (try_stream_split<S>(src, given_max, planes, expo, R, K, Kp, batch, batch_stride, st)) {
+        // one read of the operand from HBM; the zeroed maxima words stay unused
     } else {
         if (given_max)
             maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);

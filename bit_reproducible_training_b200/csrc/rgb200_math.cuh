@@ -158,20 +158,9 @@ RGB_HD uint32_t round_to_f32_bits(long long T, int E) {
 // Branch-free common case of round_to_f32_bits for unrolled epilogues: returns the result that is
 // valid when *ok stays true (the scaled value is a non-zero normal number); the caller redoes the
 // few outputs with ok == false through round_to_f32_bits.  Keeping branches out of the per-output
-// code lets the compiler interleave the independent outputs of a thread.
-__device__ __forceinline__ uint32_t round_to_f32_bits_fast(long long T, int E, bool* ok) {
-    const uint32_t sign = (uint32_t)((unsigned long long)T >> 32) & 0x80000000u;
-    const uint64_t m = (uint64_t)(T < 0 ? -T : T);
-    const uint32_t fb = f32_bits(__ull2float_rn(m));
-    const int e = (int)(fb >> 23) + E;                       // biased exponent of the scaled result
-    *ok = (unsigned)(e - 1) <= 253u;                         // 1..254: normal (m == 0 gives e = E, handled: see below)
-    if (m == 0) *ok = false;
-    return sign | (fb + ((uint32_t)E << 23));
-}
-
-// The same contract as round_to_f32_bits_fast with fewer instructions: the signed hardware conversion rounds the
-// magnitude to nearest-even and carries the sign (round-to-nearest-even is symmetric in the sign), so neither
-// the absolute value nor the sign bit has to be formed separately.
+// code lets the compiler interleave the independent outputs of a thread.  The signed hardware conversion
+// rounds the magnitude to nearest-even and carries the sign (round-to-nearest-even is symmetric in the
+// sign), so neither the absolute value nor the sign bit has to be formed separately.
 __device__ __forceinline__ uint32_t round_to_f32_bits_signed(long long T, int E, bool* ok) {
     const uint32_t fb = f32_bits(__ll2float_rn(T));
     const int e = (int)((fb >> 23) & 0xFFu) + E;             // biased exponent of the scaled result

@@ -471,10 +471,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const int ebase = ea + P.e0;
                 auto round4 = [&](int j, uint32_t (&r)[4]) {
                     bool k0, k1, k2, k3;
-                    r[0] = round_to_f32_bits_fast(T[j + 0], ebase + eb_s[j + 0], &k0);
-                    r[1] = round_to_f32_bits_fast(T[j + 1], ebase + eb_s[j + 1], &k1);
-                    r[2] = round_to_f32_bits_fast(T[j + 2], ebase + eb_s[j + 2], &k2);
-                    r[3] = round_to_f32_bits_fast(T[j + 3], ebase + eb_s[j + 3], &k3);
+                    r[0] = round_to_f32_bits_signed(T[j + 0], ebase + eb_s[j + 0], &k0);
+                    r[1] = round_to_f32_bits_signed(T[j + 1], ebase + eb_s[j + 1], &k1);
+                    r[2] = round_to_f32_bits_signed(T[j + 2], ebase + eb_s[j + 2], &k2);
+                    r[3] = round_to_f32_bits_signed(T[j + 3], ebase + eb_s[j + 3], &k3);
                     if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
                         r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
                         r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);

@@ -187,7 +187,7 @@ split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int b
 
 // Short rows (K <= 128, one padded k block per row; 16-byte aligned rows): a warp per row, and every warp walks
 // over many rows so that the grid stays small - with one row per warp the launch of tens of thousands of tiny
-// CTAs costs more than the rows' traffic.  Two rows are in flight per warp.  Same two-operand convention as
+// CTAs costs more than the rows' traffic.  Four rows are in flight per warp.  Same two-operand convention as
 // split_kmajor_kernel.  grid = (CTAs, batch); any CTA count works.
 template <int S>
 __global__ void __launch_bounds__(PREPASS_THREADS)
@@ -226,13 +226,19 @@ split_kmajor_short_kernel(const KmajorOperand first, const KmajorOperand second,
         store_quad<S>(v, quant_scale(e, S), plain_row(e), x.planes + (size_t)b * S * plane_stride + (size_t)x.r * KP, plane_stride,
                       (size_t)lane * 4);
     };
-    for (int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5); row < rows_total; row += 2 * warps_total) {
-        const bool two = row + warps_total < rows_total;
-        const RowRef x0 = locate(row), x1 = locate(two ? row + warps_total : row);
-        const float4 v0 = load(x0);
-        const float4 v1 = two ? load(x1) : make_float4(0.f, 0.f, 0.f, 0.f);
-        finish(x0, v0);
-        if (two) finish(x1, v1);
+    constexpr int INFLIGHT = 4;                  // rows whose loads are issued before the first one is consumed
+    for (int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5); row < rows_total; row += INFLIGHT * warps_total) {
+        float4 v[INFLIGHT];
+#pragma unroll
+        for (int i = 0; i < INFLIGHT; ++i) {
+            const int ri = row + i * warps_total;
+            v[i] = ri < rows_total ? load(locate(ri)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < INFLIGHT; ++i) {
+            const int ri = row + i * warps_total;
+            if (ri < rows_total) finish(locate(ri), v[i]);
+        }
     }
 }
 
@@ -297,17 +303,29 @@ colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ max
 }
 
 // Row maxima of a k-contiguous operand, written as floats (the K-sharded path's first step).
-// One warp per row.  grid = ceil(R / 8).
+// One warp per row; 16-byte loads, four in flight per lane, when the rows are 16-byte aligned.  grid = ceil(R / 8).
 __global__ void __launch_bounds__(PREPASS_THREADS)
 rowmax_kmajor_kernel(const float* __restrict__ src, float* __restrict__ out, int R, int K) {
     const int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5);
     if (row >= R) return;
+    const int lane = threadIdx.x & 31;
     const float* a = src + (size_t)row * K;
     float m = 0.f;
-    for (int k = threadIdx.x & 31; k < K; k += 32) m = fmaxf(m, fabsf(__ldg(a + k)));
+    if ((K & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const float4* a4 = reinterpret_cast<const float4*>(a);
+        const int nq = K >> 2;
+        int c = lane;
+        for (; c + 96 < nq; c += 128) {
+            const float4 v0 = __ldg(a4 + c), v1 = __ldg(a4 + c + 32), v2 = __ldg(a4 + c + 64), v3 = __ldg(a4 + c + 96);
+            m = abs4max(abs4max(abs4max(abs4max(m, v0), v1), v2), v3);
+        }
+        for (; c < nq; c += 32) m = abs4max(m, __ldg(a4 + c));
+    } else {
+        for (int k = lane; k < K; k += 32) m = fmaxf(m, fabsf(__ldg(a + k)));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if ((threadIdx.x & 31) == 0) out[row] = m;
+    if (lane == 0) out[row] = m;
 }
 
 // Pass 2 for the k-strided operand: 32 (r) x 128 (k) tiles are read with r contiguous (16-byte loads

@@ -15,18 +15,24 @@
 //           would have produced - one k block (two chunks) per MMA stage;
 //   MMA     one thread issues the same level-accumulating MMAs as the general kernel;
 //   finish  the sixteen warps drain TMEM, rebuild the exact sums, round once and store C.
-// Because the copies are asynchronous the chunks of pass 1, pass 2 and of the next tile follow each other
-// without the warps ever waiting for a load they issued themselves.
+// The chunks of a tile's pass 2 alternate with those of the next tile's pass 1, so the next tile's reads from
+// HBM are in flight while this tile's values are being converted, and the warps never wait for a load they
+// issued themselves.
 // The arithmetic is that of the general kernel (rgb200_mma.cuh) and of the split pre-pass
 // (rgb200_prepass.cuh); only where the digits of A live differs.  Reference counterparts:
 // quantize_kmajor + gemm_wmma_i8 (repro_gemm_cuda/repro_gemm.cu:54-79, 280-364).
 #pragma once
 #include "rgb200_mma.cuh"
 #include "rgb200_prepass.cuh"
-#include "rgb200_prepass_cluster.cuh"
 #include "rgb200_smallk.cuh"
 
 namespace rgb200 {
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 
 constexpr int RF_NT = 64;                     // columns of C per tile (one tile covers all of N)
 constexpr int RF_A_STAGES = 2;                // int8 stages the MMA reads (one k block each)
@@ -132,16 +138,28 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 ++f_it;
                 return true;
             };
+            // chunk order (the work warps consume in the same order): pass 1 of the CTA's first tile; then, per tile,
+            // for every half k block its pass-2 chunk followed by the same chunk of the NEXT tile for that tile's
+            // pass 1, so that the next tile's HBM reads overlap this tile's conversion work
+            if ((int)blockIdx.x < total_tiles) {
+                const int batch = blockIdx.x / P.m_tiles, m_blk = blockIdx.x - batch * P.m_tiles;
+                for (int c = 0; ok && c < 2 * P.k_blocks; ++c) ok = load_chunk(c, m_blk, batch);
+            }
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
-                for (int c = 0; ok && c < 2 * P.k_blocks; ++c) ok = load_chunk(c, m_blk, batch);          // pass 1
-                for (int kb = 0; ok && kb < P.k_blocks; ++kb) {                                            // pass 2
+                const int next = tile + gridDim.x;
+                const bool has_next = next < total_tiles;
+                const int n_batch = has_next ? next / P.m_tiles : 0, n_blk = has_next ? next - n_batch * P.m_tiles : 0;
+                for (int kb = 0; ok && kb < P.k_blocks; ++kb) {
                     const int s = b_it % RF_B_STAGES;
                     if (!(ok = mbar_wait(b_empty(s), ((b_it / RF_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                     mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
                     tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), kb * BLOCK_K, 0, 0, batch);
                     ++b_it;
-                    ok = load_chunk(2 * kb, m_blk, batch) && load_chunk(2 * kb + 1, m_blk, batch);
+                    for (int h = 0; ok && h < 2; ++h) {
+                        ok = load_chunk(2 * kb + h, m_blk, batch);
+                        if (ok && has_next) ok = load_chunk(2 * kb + h, n_blk, n_batch);
+                    }
                 }
             }
             if (!ok) {
@@ -165,7 +183,6 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
-            constexpr uint32_t IDESC_ONE = idesc_i8(BLOCK_M, NT);
             uint32_t it = 0, tile_it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
@@ -181,12 +198,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         if (kb == 0 && k == 0) {
-#pragma unroll
-                            for (int p = 0; p < S; ++p)
-#pragma unroll
-                                for (int q = 0; q < S; ++q)
-                                    umma_i8(tmem_base + (p + q) * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES),
-                                            smem_desc_sw128(sb + q * Tr::B_PLANE_BYTES), IDESC_ONE, (p != 0 && q != S - 1) ? 1u : 0u);
+                            issue_first_k_step<S, NT>(tmem_base, sa, sb, Tr::A_PLANE_BYTES, Tr::B_PLANE_BYTES);
                         } else {
 #pragma unroll
                             for (int p = 0; p < S; ++p)
@@ -214,25 +226,29 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const int rsel = lane >> 4;
         uint32_t f_it = 0, a_it = 0, tile_it = 0;
         bool ok = true;
+        // one FP32 chunk into the running row maxima
+        auto max_chunk = [&](float (&m)[4]) {
+            const int s = f_it % RF_F_STAGES;
+            bool got = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+            got = __all_sync(0xFFFFFFFFu, got);
+            if (!got) return false;
+            const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = cw * 8 + i + 4 * rsel;
+                m[i] = abs4max(m[i], *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + c16 * 16));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(f_empty(s));
+            ++f_it;
+            return true;
+        };
+        float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if ((int)blockIdx.x < total_tiles)                 // pass 1 of the first tile
+            for (int c = 0; ok && c < 2 * P.k_blocks; ++c) ok = max_chunk(m);
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
             const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
-            // pass 1: row maxima
-            float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            for (int c = 0; c < 2 * P.k_blocks; ++c, ++f_it) {
-                const int s = f_it % RF_F_STAGES;
-                ok = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
-                ok = __all_sync(0xFFFFFFFFu, ok);
-                if (!ok) break;
-                const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = cw * 8 + i + 4 * rsel;
-                    m[i] = abs4max(m[i], *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + c16 * 16));
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(f_empty(s));
-            }
-            if (!ok) break;
+            const bool has_next = tile + (int)gridDim.x < total_tiles;
             int e[4];
             float f1[4];
             bool all_plain = true;
@@ -244,9 +260,10 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 f1[i] = quant_scale(e[i], S).f1;
                 all_plain = all_plain && plain_row(e[i]);
                 if (c16 == 0) ea_rows[cw * 8 + i + 4 * rsel] = e[i];    // the previous tile's epilogue has finished reading (done_bar)
+                m[i] = 0.0f;                                            // now collects the next tile's maxima
             }
             all_plain = __all_sync(0xFFFFFFFFu, all_plain);
-            // pass 2: digits into the swizzled stages
+            // pass 2: digits into the swizzled stages, interleaved chunk by chunk with pass 1 of the next tile
             for (int kb = 0; kb < P.k_blocks; ++kb, ++a_it) {
                 const int sa_i = a_it % RF_A_STAGES;
                 ok = mbar_wait(a_empty(sa_i), ((a_it / RF_A_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY);
@@ -254,7 +271,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (!ok) break;
                 uint8_t* stage = gen_a + sa_i * Tr::A_STAGE_BYTES;
 #pragma unroll
-                for (int h = 0; h < 2; ++h, ++f_it) {
+                for (int h = 0; h < 2; ++h) {
                     const int s = f_it % RF_F_STAGES;
                     ok = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
                     ok = __all_sync(0xFFFFFFFFu, ok);
@@ -275,6 +292,8 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(f_empty(s));
+                    ++f_it;
+                    if (has_next && !(ok = max_chunk(m))) break;
                 }
                 if (!ok) break;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> visible to the MMA's reads

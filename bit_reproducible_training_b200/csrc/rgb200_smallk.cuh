@@ -5,9 +5,12 @@
 // 2S-1 TMEM reads, the INT64 recombination, one rounding and four bytes of C per output.  The
 // general kernel cannot overlap that work with the next tile's MMAs at S = 3 (its 128 x 64 tile fills
 // 320 of the 512 TMEM columns), so this one is organised around the epilogue instead:
-//   * 128 x 32 tiles: the (2S-1) * 32 accumulator columns fit TMEM twice.  Two groups of eight
+//   * 128 x 48 tiles: the (2S-1) * 48 accumulator columns fit TMEM twice.  Two groups of eight
 //     epilogue warps own one accumulator set each and alternate tiles, so sixteen warps drain, round
 //     and store while the MMA warp is already one or two tiles ahead.
+//   * few, wide MMAs: the single issuing thread needs on the order of a hundred cycles per MMA whatever its
+//     size, so a tile's first k step takes 2S-1 MMAs (see issue_first_k_step) instead of S^2, and the
+//     48-column tile spreads that cost over half as many more outputs than a 32-column one would.
 //   * A-stationary: a CTA walks a contiguous range of tiles with the column tile running fastest, so
 //     the 128-row A tile (all S planes, the whole K) is loaded once per row of tiles into one of two
 //     buffers; only the small B tiles stream through a ring of stages.
@@ -20,8 +23,8 @@
 
 namespace rgb200 {
 
-constexpr int SK_NT = 32;                     // columns of C per tile
-constexpr int SK_B_STAGES = 6;
+constexpr int SK_NT = 48;                     // columns of C per tile
+constexpr int SK_B_STAGES = 5;
 constexpr int SK_EPI_GROUPS = 2;              // one per accumulator set
 constexpr int SK_GROUP_WARPS = 8;
 constexpr int SK_GROUP_THREADS = SK_GROUP_WARPS * 32;
@@ -48,6 +51,23 @@ combine_levels_short_k(const int (&lv)[2 * S - 1][8], int j) {
         const int low = lv[4][j] + lv[3][j] * 128;
         const int mid = lv[2][j] + lv[1][j] * 128;
         return (long long)low + (long long)mid * 16384 + (long long)lv[0][j] * 268435456ll;
+    }
+}
+
+// First k step of a tile: level L = p + q is written for the first time by (p = 0, q = L) or, for L >= S, by
+// (p = L - S + 1, q = S - 1), and accumulated into by every other pair.  So A plane 0 takes one MMA over all S
+// planes of B that overwrites levels 0..S-1, and every further A plane p one MMA over B planes 0..S-2 that
+// accumulates into levels p..p+S-2 plus one over B plane S-1 that overwrites the new level p+S-1:
+// 2S-1 MMAs.  sa / sb: shared-memory addresses of the operands' plane 0 at this k step.
+template <int S, int NT>
+__device__ __forceinline__ void issue_first_k_step(uint32_t acc, uint32_t sa, uint32_t sb, uint32_t a_plane_bytes,
+                                                   uint32_t b_plane_bytes) {
+    umma_i8(acc, smem_desc_sw128(sa), smem_desc_sw128(sb), idesc_i8(BLOCK_M, S * NT), 0u);
+#pragma unroll
+    for (int p = 1; p < S; ++p) {
+        umma_i8(acc + p * NT, smem_desc_sw128(sa + p * a_plane_bytes), smem_desc_sw128(sb), idesc_i8(BLOCK_M, (S - 1) * NT), 1u);
+        umma_i8(acc + (p + S - 1) * NT, smem_desc_sw128(sa + p * a_plane_bytes), smem_desc_sw128(sb + (S - 1) * b_plane_bytes),
+                idesc_i8(BLOCK_M, NT), 0u);
     }
 }
 
@@ -167,7 +187,6 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
-            constexpr uint32_t IDESC_ONE = idesc_i8(BLOCK_M, NT);
             uint32_t a_it = 0, b_it = 0;
             long long prev_group = -1;
             uint32_t sa = 0, cur_ab = 0;
@@ -188,13 +207,7 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 tc_fence_after();
                 const uint32_t sb = b_base + s * Tr::B_STAGE_BYTES;
                 const uint32_t acc = tmem_base + g * Tr::ACC_COLS;
-                // first k step: every level block needs its own overwrite flag
-#pragma unroll
-                for (int p = 0; p < S; ++p)
-#pragma unroll
-                    for (int q = 0; q < S; ++q)
-                        umma_i8(acc + (p + q) * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES),
-                                smem_desc_sw128(sb + q * Tr::B_PLANE_BYTES), IDESC_ONE, (p != 0 && q != S - 1) ? 1u : 0u);
+                issue_first_k_step<S, NT>(acc, sa, sb, Tr::A_PLANE_BYTES, Tr::B_PLANE_BYTES);
                 for (int k = 1; k < P.k_steps; ++k)
 #pragma unroll
                     for (int p = 0; p < S; ++p)

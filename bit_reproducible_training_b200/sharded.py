@@ -113,47 +113,60 @@ class FusedKShard:
         elems = rg.scatter_buffer_elems(M, N, self.world, cfg.slices)
         if elems == 0:
             raise ValueError("the fused K-shard needs M to be a multiple of 128 * world and at most 8 ranks")
-        self.M, self.N, self.cfg, self.rows = M, N, cfg, M // self.world
+        self.M, self.N, self.cfg, self.rows, self.elems = M, N, cfg, M // self.world, elems
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.slots = symm_mem.empty((elems,), dtype=torch.int64, device=dev)
+        # two receive buffers used in turn: a rank that is one product ahead stores into the other buffer, so a
+        # slow owner can still be reading the previous product's slots (a rank cannot get two products ahead,
+        # because each product ends with a collective every rank takes part in)
+        self.slots = symm_mem.empty((2 * elems,), dtype=torch.int64, device=dev)
         self.handle = symm_mem.rendezvous(self.slots, self.group)
-        self.owner_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.owner_ptrs = [[int(p) + half * elems * 8 for p in self.handle.buffer_ptrs] for half in (0, 1)]
+        self.phase = 0
         self.token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.maxima = torch.empty(M + N, dtype=torch.float32, device=dev)
-        self.launches_per_step = 7     # row max, column max, split A, maxima->bits + split B, MMA, rounding
+        self.launches_per_step = 7     # row max, column max, split A, split B, MMA, rounding (+ one more when B's split takes two kernels)
 
-    def __call__(self, A_k, B_k, k_local, total_k, out=None):
+    def __call__(self, A_k, B_k, k_local, total_k, out=None, gather=True):
+        """gather=True: the full C on every rank (FP32 all-gather of the owners' rows).  gather=False: only this rank's
+        rows [rank * M / world, (rank + 1) * M / world) are returned, for callers that go on row-sharded."""
         cfg, M, N = self.cfg, self.M, self.N
+        half = self.phase
+        self.phase ^= 1
         # one buffer for both sets of maxima: a single max all-reduce instead of two
         maxima = self.maxima
         rg.absmax(A_k, M, k_local, cfg.trans_a, out=maxima[:M])
         rg.absmax(B_k, N, k_local, not cfg.trans_b, out=maxima[M:])
         dist.all_reduce(maxima, op=dist.ReduceOp.MAX, group=self.group)
         max_a, max_b = maxima[:M], maxima[M:]
-        rg.gemm_partial_scatter(A_k, B_k, max_a, max_b, self.owner_ptrs, self.world, self.rank, M, N, k_local, total_k, cfg)
+        rg.gemm_partial_scatter(A_k, B_k, max_a, max_b, self.owner_ptrs[half], self.world, self.rank, M, N, k_local, total_k, cfg)
         # stream-ordered barrier: no rank reads its slots before every rank's kernel has finished writing them
         dist.all_reduce(self.token, group=self.group)
         lo = self.rank * self.rows
-        C_own = rg.round_scattered(self.slots, self.world, max_a[lo:lo + self.rows], max_b, self.rows, N, cfg.slices)
+        own = self.slots[half * self.elems:(half + 1) * self.elems]
+        if not gather:
+            return rg.round_scattered(own, self.world, max_a[lo:lo + self.rows], max_b, self.rows, N, cfg.slices,
+                                      out=out)
+        C_own = rg.round_scattered(own, self.world, max_a[lo:lo + self.rows], max_b, self.rows, N, cfg.slices)
         C = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=C_own.device)
-        # the gather also keeps a fast rank's next product from overwriting slots a slow owner still reads
         dist.all_gather_into_tensor(C.view(M, N), C_own, group=self.group)
         return C
 
 
 class KSplitState:
     """Benchmark helper: this rank's operands are one K range of an M x N x (K * world) product."""
-    launches_per_step = 8   # row max, column max, split A, maxima->bits + split B, MMA, rounding (+ the memset)
+    launches_per_step = 7   # row max, column max, split A, split B, MMA, rounding (+ one more when B's split takes two kernels)
 
-    def __init__(self, M, N, K, world, cfg, dA, dB, fused=False):
+    def __init__(self, M, N, K, world, cfg, dA, dB, fused=False, gather=True):
         self.M, self.N, self.K, self.world, self.cfg, self.dA, self.dB = M, N, K, world, cfg, dA, dB
         self.fused = FusedKShard(M, N, cfg) if fused else None
+        self.gather = gather
         if self.fused is not None:
             self.launches_per_step = self.fused.launches_per_step
 
     def step(self, dC):
+        """dC: the full C (gather=True) or this rank's rows of it (fused form with gather=False)."""
         if self.fused is not None:
-            self.fused(self.dA, self.dB, self.K, self.K * self.world, out=dC)
+            self.fused(self.dA, self.dB, self.K, self.K * self.world, out=dC, gather=self.gather)
             return
         out = gemm_k_sharded(self.dA, self.dB, self.M, self.N, self.K, self.K * self.world, self.cfg)
         dC.copy_(out.reshape(-1))

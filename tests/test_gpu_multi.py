@@ -55,10 +55,16 @@ def worker(rank, world, port, n, want_hash, out_dir):
         assert "%016x" % rg.fnv1a64(C_t) == want_hash, "K-sharded (transposed storage) result differs"
         # K ranges with the reduction started inside the MMA epilogue (peer stores into the row owners)
         fused = sharded.FusedKShard(n, n, cfg)
-        for _ in range(2):
-            C_f = fused(torch.from_numpy(np.ascontiguousarray(A[:, klo:khi])).cuda(),
-                        torch.from_numpy(np.ascontiguousarray(B[klo:khi])).cuda(), khi - klo, n)
+        A_k = torch.from_numpy(np.ascontiguousarray(A[:, klo:khi])).cuda()
+        B_k = torch.from_numpy(np.ascontiguousarray(B[klo:khi])).cuda()
+        for _ in range(3):              # the two receive buffers alternate
+            C_f = fused(A_k, B_k, khi - klo, n)
             assert "%016x" % rg.fnv1a64(C_f) == want_hash, "fused K-shard result differs"
+        # row-sharded output: every rank keeps its own rows only, back to back without a gather in between
+        rows = n // world
+        for _ in range(3):
+            C_own = fused(A_k, B_k, khi - klo, n, gather=False)
+            assert torch.equal(C_own.view(torch.int32), C_f.view(n, n)[rank * rows:(rank + 1) * rows].view(torch.int32))
         torch.cuda.synchronize()
         open(os.path.join(out_dir, "ok.%d" % rank), "w").close()
     finally:
