@@ -15,7 +15,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "librgb200.so")
 SOURCES = ["rgb200_api.cu", "rgb200_cxx.cu"]
 HEADERS = ["rgb200_math.cuh", "rgb200_mma.cuh", "rgb200_smallk.cuh", "rgb200_rowfused.cuh", "rgb200_prepass.cuh",
-           "rgb200_prepass_stream.cuh", "rgb200_conv.cuh",
+           "rgb200_prepass_cluster.cuh", "rgb200_conv.cuh", "rgb200_conv_direct.cuh",
            os.path.join("..", "..", "include", "rgb200.h"), os.path.join("..", "..", "include", "repro_gemm.cuh"),
            os.path.join("..", "..", "include", "repro_conv.cuh")]
 

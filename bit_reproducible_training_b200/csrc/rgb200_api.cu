@@ -19,8 +19,9 @@
 #include "rgb200_smallk.cuh"
 #include "rgb200_rowfused.cuh"
 #include "rgb200_prepass.cuh"
-#include "rgb200_prepass_stream.cuh"
+#include "rgb200_prepass_cluster.cuh"
 #include "rgb200_conv.cuh"
+#include "rgb200_conv_direct.cuh"
 
 namespace rgb200 {
 namespace {
@@ -154,6 +155,15 @@ cudaError_t set_kernel_attrs() {
                                 GemmTraits<S, NT>::SMEM_BYTES);
 }
 
+template <int S>
+cudaError_t set_cluster_split_attrs() {
+    const int bytes = KSC_MAX_SLAB_BYTES + 128;
+    cudaError_t e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(split_kstrided_cluster_kernel<S, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e;
+}
+
 cudaError_t device_info(const DeviceInfo** out) {
     int dev;
     cudaError_t e = cudaGetDevice(&dev);
@@ -187,6 +197,11 @@ cudaError_t device_info(const DeviceInfo** out) {
             if ((e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<1>::SMEM_BYTES)) != cudaSuccess ||
                 (e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<2>::SMEM_BYTES)) != cudaSuccess ||
                 (e2 = cudaFuncSetAttribute(gemm_i8_rowfused_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowFusedTraits<3>::SMEM_BYTES)) != cudaSuccess) {
+                d.err = e2;
+                return;
+            }
+            if ((e2 = set_cluster_split_attrs<1>()) != cudaSuccess || (e2 = set_cluster_split_attrs<2>()) != cudaSuccess ||
+                (e2 = set_cluster_split_attrs<3>()) != cudaSuccess) {
                 d.err = e2;
                 return;
             }
@@ -242,6 +257,19 @@ cudaError_t encode_planes_map(CUtensorMap* map, const void* planes, int rows, in
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// FP32 operand stored [batch][K][R] (r contiguous), as the cluster split reads it: dims (r, k, batch), box (W, 64, 1).
+cudaError_t encode_kstrided_map(CUtensorMap* map, const float* src, int R, int K, int batch, long long batch_stride, int W) {
+    if (!ensure_encode()) return cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)K, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)R * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)R * K) * 4};
+    cuuint32_t box[3] = {(cuuint32_t)W, (cuuint32_t)KSC_BOX_K, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(src), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 // FP32 operand stored [batch][M][K] (k contiguous), as the fused-split kernel streams it: dims (k, row, batch),
 // box (64 k, 128 rows, 1), zero fill beyond K and M.
 cudaError_t encode_kmajor_f32_map(CUtensorMap* map, const float* src, int M, int K, int batch, long long batch_stride) {
@@ -256,18 +284,45 @@ cudaError_t encode_kmajor_f32_map(CUtensorMap* map, const float* src, int M, int
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-// The one-kernel form of the k-strided split (rgb200_prepass_stream.cuh): a cluster of eight CTAs per 32 columns.
-// Used when there are enough columns to fill the GPU that way; operands with few columns and a long K keep the
-// two-kernel form, which also spreads the work over k.
+// The cluster form of the k-strided split (one read of the operand, rgb200_prepass_cluster.cuh).  Returns false when
+// the operand cannot take it (rows not a multiple of four floats, unaligned base or batch stride, K too long for a
+// slab), and the caller then runs the two-kernel form.  `overlap`: launch with programmatic stream serialization,
+// so that the kernel may start while the previous kernel of the stream - the other operand's split, which it does
+// not depend on - is still draining; the next ordinary launch of the stream waits for both, as stream order demands.
+template <int S, int W>
+cudaError_t launch_cluster_split(const CUtensorMap& map, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp,
+                                 int KC, int batch, int* status, bool overlap, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(KSC_CLUSTER * ceil_div(R, W), batch);
+    cfg.blockDim = dim3(PREPASS_THREADS);
+    cfg.dynamicSmemBytes = (size_t)KC * W * 4 + 128;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, split_kstrided_cluster_kernel<S, W>, map, given_max, planes, expo, R, K, Kp, KC, status);
+}
+
 template <int S>
-bool try_stream_split(const float* src, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp, int batch,
-                      long long batch_stride, cudaStream_t st) {
-    const long long ctas = (long long)ceil_div(R, KSS_W) * KSS_CLUSTER * batch;
-    if (ctas < 64) return false;
-    const int KC = ceil_div(ceil_div(Kp, KSS_CLUSTER), 32) * 32;
-    split_kstrided_stream_kernel<S><<<dim3(KSS_CLUSTER * ceil_div(R, KSS_W), batch), PREPASS_THREADS, 0, st>>>(
-        src, given_max, planes, expo, R, K, Kp, KC, batch_stride);
-    return true;
+bool try_cluster_split(const float* src, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp, int batch,
+                       long long batch_stride, int* status, bool overlap, cudaStream_t st) {
+    if (R % 4 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0 || (batch > 1 && batch_stride % 4 != 0)) return false;
+    if (!ensure_encode()) return false;
+    const int KC = ceil_div(ceil_div(Kp, KSC_CLUSTER), KSC_BOX_K) * KSC_BOX_K;
+    int W = 32;
+    while (W > 8 && (size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) W >>= 1;
+    if ((size_t)KC * W * 4 > (size_t)KSC_MAX_SLAB_BYTES) return false;
+    while (W > 8 && (long long)ceil_div(R, W) * KSC_CLUSTER * batch < PLAN_SM_COUNT) W >>= 1;   // few columns: narrower panels, more CTAs
+    CUtensorMap map;
+    if (encode_kstrided_map(&map, src, R, K, batch, batch_stride, W) != cudaSuccess) return false;
+    cudaError_t e;
+    if (W == 32) e = launch_cluster_split<S, 32>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, overlap, st);
+    else if (W == 16) e = launch_cluster_split<S, 16>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, overlap, st);
+    else e = launch_cluster_split<S, 8>(map, given_max, planes, expo, R, K, Kp, KC, batch, status, overlap, st);
+    if (e != cudaSuccess) (void)cudaGetLastError();      // not launched: the caller falls back to the two-kernel form
+    return e == cudaSuccess;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -295,7 +350,8 @@ void launch_kmajor(const KmajorOperand& first, const KmajorOperand& second, int 
         const long long rows = (long long)first.R + (two ? second.R : 0);
         const long long want = (rows + 63) / 64;         // eight rows per warp at least
         const int ctas = (int)(want < 1 ? 1 : (want > PLAN_SM_COUNT * 8 ? PLAN_SM_COUNT * 8 : want));
-        split_kmajor_short_kernel<S><<<dim3(ctas, batch), PREPASS_THREADS, 0, st>>>(first, second, K, zero_word);
+        if (K <= 64) split_kmajor_short_kernel<S, true><<<dim3(ctas, batch), PREPASS_THREADS, 0, st>>>(first, second, K, zero_word);
+        else split_kmajor_short_kernel<S, false><<<dim3(ctas, batch), PREPASS_THREADS, 0, st>>>(first, second, K, zero_word);
         return;
     }
     if (!aligned || nq > 256 * KMAJOR_MAX_CHUNKS) {      // general path: any K, any alignment; row group sized to the row
@@ -317,13 +373,13 @@ void launch_kmajor(const KmajorOperand& first, const KmajorOperand& second, int 
 // One operand through the pre-pass.  k_major: element (r, k) at src[r*K + k].
 template <int S>
 void launch_split(const float* src, bool k_major, const float* given_max, uint32_t* maxbits, int8_t* planes, int* expo,
-                  int R, int K, int Kp, int batch, long long batch_stride, int* status, cudaStream_t st) {
+                  int R, int K, int Kp, int batch, long long batch_stride, int* status, cudaStream_t st, bool overlap = false) {
     if (k_major) {
         const KmajorOperand op{src, given_max, planes, expo, R, batch_stride};
         const KmajorOperand none{nullptr, nullptr, nullptr, nullptr, 0, 0};
         launch_kmajor<S>(op, none, K, Kp, batch, nullptr, st);
-    } else if (try_stream_split<S>(src, given_max, planes, expo, R, K, Kp, batch, batch_stride, st)) {
-        // one read of the operand from HBM; the zeroed maxima words stay unused
+    } else if (try_cluster_split<S>(src, given_max, planes, expo, R, K, Kp, batch, batch_stride, status, overlap, st)) {
+        // one read of the operand; the zeroed maxima words stay unused
     } else {
         if (given_max)
             maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);
@@ -451,7 +507,7 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         // both splits on the caller's stream, one after the other: each saturates the memory system by itself, and
         // the library keeps no stream or event of its own
         launch_split<S>(a.A, !a.trans_a, a.max_a, max_a, qa, ea, L.M, L.K, L.Kp, L.batch, a.stride_a, status, a.st);
-        launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, status, a.st);
+        launch_split<S>(a.B, a.trans_b, a.max_b, max_b, qb, eb, L.N, L.K, L.Kp, L.batch, a.stride_b, status, a.st, true);
         record(1);
     }
 
@@ -734,6 +790,39 @@ cudaError_t conv_run(ConvKind kind, const float* p, const float* q, float* out, 
     if (!p || !q || !out || !ws || ws_bytes < L.total + conv_extra_bytes(kind, g)) return cudaErrorInvalidValue;
     const DeviceInfo* dev = nullptr;
     if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
+    // The smallest layers (a LeNet-style first convolution) skip the tensor cores: one thread per output
+    // evaluates the definition directly (rgb200_conv_direct.cuh).  Scratch - the fixed-point weights and the
+    // exponents - sits where the implicit-GEMM path would put A's digit planes.
+    {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        int* scratch = reinterpret_cast<int*>(static_cast<char*>(ws) + L.qa);
+        const size_t room = L.total - L.qa;
+        const long long weights = (long long)g.F * g.K;
+        if (kind == CONV_FORWARD && g.K <= CONV_DIRECT_MAX_K && g.F <= CONV_DIRECT_MAX_F &&
+            room >= (size_t)(weights + g.F) * sizeof(int)) {
+            int* wq = scratch;
+            int* ef = scratch + weights;
+            const long long windows = (long long)g.N * g.OH * g.OW;
+            #define RGB_CONV_FWD(SS) do { \
+                conv_direct_filters_kernel<SS><<<1, 32 * g.F, 0, st>>>(q, wq, ef, g.F, g.K); \
+                conv_direct_forward_kernel<SS><<<(unsigned)((windows + CONV_DIRECT_THREADS - 1) / CONV_DIRECT_THREADS), CONV_DIRECT_THREADS, 0, st>>>(p, wq, ef, out, g); } while (0)
+            if (S == 1) RGB_CONV_FWD(1); else if (S == 2) RGB_CONV_FWD(2); else RGB_CONV_FWD(3);
+            #undef RGB_CONV_FWD
+            return cudaGetLastError();
+        }
+        if (kind == CONV_GRAD_INPUT && weights <= CONV_DIRECT_MAX_WEIGHTS && (long long)g.F * g.KH * g.KW <= 256 &&
+            room >= (size_t)(weights + g.N + 1) * sizeof(int)) {
+            int* wq = scratch;
+            int* e_img = scratch + weights;
+            const long long pixels = (long long)g.N * g.C * g.H * g.W;
+            #define RGB_CONV_DX(SS) do { \
+                conv_direct_grad_input_scales_kernel<SS><<<g.N + 1, 256, 0, st>>>(p, q, e_img, wq, g.N, g.F * g.OH * g.OW, (int)weights); \
+                conv_direct_grad_input_kernel<SS><<<(unsigned)((pixels + CONV_DIRECT_THREADS - 1) / CONV_DIRECT_THREADS), CONV_DIRECT_THREADS, 0, st>>>(p, wq, e_img, out, g); } while (0)
+            if (S == 1) RGB_CONV_DX(1); else if (S == 2) RGB_CONV_DX(2); else RGB_CONV_DX(3);
+            #undef RGB_CONV_DX
+            return cudaGetLastError();
+        }
+    }
     const ConvCall call{kind, g, p, q, conv_rows_are_places(kind, g, S),
                         reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + L.total)};
     const PrepassHook hook{conv_prepass, &call};
@@ -899,7 +988,7 @@ int rgb200_gemm_fp32_batched_ws(const float* A, const float* B, float* C, int M,
 int rgb200_host_gemm_create(int M, int N, int K, const rgb200_config* cfg, int block_rows, rgb200_host_gemm** handle) {
     if (!handle || !cfg) return cudaErrorInvalidValue;
     *handle = nullptr;
-    if (block_rows <= 0) block_rows = 512;
+    if (block_rows <= 0) block_rows = 256;
     rgb200_host_gemm* h = new (std::nothrow) rgb200_host_gemm();
     if (!h) return cudaErrorMemoryAllocation;
     h->M = M; h->N = N; h->K = K; h->cfg = *cfg;

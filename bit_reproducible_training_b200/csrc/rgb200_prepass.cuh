@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(PREPASS_THREADS)
 split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int blocks_first,
                     int K, int Kp, int* zero_word) {
     __shared__ float red[PREPASS_THREADS / 32];
+    // the other operand's split, if launched behind this kernel with programmatic serialization, may start now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int rows_per_cta = PREPASS_THREADS / TPR;
     if (zero_word && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *zero_word = 0;
     const bool is_first = (int)blockIdx.x < blocks_first;
@@ -185,20 +187,25 @@ split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int b
     }
 }
 
-// Short rows (K <= 128, one padded k block per row; 16-byte aligned rows): a warp per row, and every warp walks
-// over many rows so that the grid stays small - with one row per warp the launch of tens of thousands of tiny
-// CTAs costs more than the rows' traffic.  Four rows are in flight per warp.  Same two-operand convention as
-// split_kmajor_kernel.  grid = (CTAs, batch); any CTA count works.
-template <int S>
+// Short rows (K <= 128, one padded k block per row; 16-byte aligned rows): a warp per row - or, for K <= 64, a
+// half-warp per row, so that every lane loads - and every warp walks over many rows so that the grid stays
+// small: the per-row work (maximum, exponent, scale) is a large part of the cost of so short a row, and with
+// one row per warp the launch of tens of thousands of tiny CTAs costs more than the rows' traffic.  Four row
+// slots are in flight per warp.  Same two-operand convention as split_kmajor_kernel.
+// grid = (CTAs, batch); any CTA count works.
+template <int S, bool HALF>
 __global__ void __launch_bounds__(PREPASS_THREADS)
 split_kmajor_short_kernel(const KmajorOperand first, const KmajorOperand second, int K, int* zero_word) {
     constexpr int KP = 128;
+    constexpr int LANES = HALF ? 16 : 32;                 // lanes per row
+    constexpr int RPW = 32 / LANES;                       // rows per warp and slot
     if (zero_word && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *zero_word = 0;
     const int lane = threadIdx.x & 31;
+    const int c = lane % LANES, sub = lane / LANES;
     const int b = blockIdx.y;
     const int nq = K >> 2;
     const int rows_total = first.R + second.R;
-    const int warps_total = gridDim.x * (PREPASS_THREADS / 32);
+    const int slots_total = gridDim.x * (PREPASS_THREADS / 32) * RPW;     // rows handled side by side
     // the operand's fields are picked one by one (a pointer to a kernel parameter would force it into local memory)
     struct RowRef { const float* src; const float* given_max; int8_t* planes; int* expo; int R; int r; };
     auto locate = [&](int row) {
@@ -213,31 +220,38 @@ split_kmajor_short_kernel(const KmajorOperand first, const KmajorOperand second,
         return x;
     };
     auto load = [&](const RowRef& x) {
-        return lane < nq ? __ldg(reinterpret_cast<const float4*>(x.src) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        return c < nq ? __ldg(reinterpret_cast<const float4*>(x.src) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
     };
-    auto finish = [&](const RowRef& x, float4 v) {
+    auto finish = [&](const RowRef& x, float4 v, bool valid) {
         float m = abs4max(0.0f, v);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        for (int o = LANES / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));     // over the row's lanes
+        if (!valid) return;
         if (x.given_max) m = x.given_max[(size_t)b * x.R + x.r];
         const int e = scale_exponent(m);
-        if (lane == 0) x.expo[(size_t)b * x.R + x.r] = e;
+        if (c == 0) x.expo[(size_t)b * x.R + x.r] = e;
         const size_t plane_stride = (size_t)x.R * KP;
-        store_quad<S>(v, quant_scale(e, S), plain_row(e), x.planes + (size_t)b * S * plane_stride + (size_t)x.r * KP, plane_stride,
-                      (size_t)lane * 4);
+        int8_t* out = x.planes + (size_t)b * S * plane_stride + (size_t)x.r * KP;
+        store_quad<S>(v, quant_scale(e, S), plain_row(e), out, plane_stride, (size_t)c * 4);
+        if (HALF) {                                       // k 64..127 of the padded row: zeros
+#pragma unroll
+            for (int p = 0; p < S; ++p) *reinterpret_cast<uint32_t*>(out + p * plane_stride + 64 + c * 4) = 0u;
+        }
     };
-    constexpr int INFLIGHT = 4;                  // rows whose loads are issued before the first one is consumed
-    for (int row = blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5); row < rows_total; row += INFLIGHT * warps_total) {
+    constexpr int INFLIGHT = 4;                           // row slots whose loads are issued before the first one is consumed
+    const int first_row = (blockIdx.x * (PREPASS_THREADS / 32) + (threadIdx.x >> 5)) * RPW + sub;
+    // every lane of a warp runs the same number of iterations (the shuffles need the whole warp)
+    for (int base = first_row - sub; base < rows_total; base += INFLIGHT * slots_total) {
         float4 v[INFLIGHT];
 #pragma unroll
         for (int i = 0; i < INFLIGHT; ++i) {
-            const int ri = row + i * warps_total;
+            const int ri = base + sub + i * slots_total;
             v[i] = ri < rows_total ? load(locate(ri)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int i = 0; i < INFLIGHT; ++i) {
-            const int ri = row + i * warps_total;
-            if (ri < rows_total) finish(locate(ri), v[i]);
+            const int ri = base + sub + i * slots_total;
+            finish(locate(ri < rows_total ? ri : 0), v[i], ri < rows_total);
         }
     }
 }

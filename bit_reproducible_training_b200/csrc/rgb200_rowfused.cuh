@@ -15,9 +15,9 @@
 //           would have produced - one k block (two chunks) per MMA stage;
 //   MMA     one thread issues the same level-accumulating MMAs as the general kernel;
 //   finish  the sixteen warps drain TMEM, rebuild the exact sums, round once and store C.
-// The chunks of a tile's pass 2 alternate with those of the next tile's pass 1, so the next tile's reads from
-// HBM are in flight while this tile's values are being converted, and the warps never wait for a load they
-// issued themselves.
+// Shared memory holds only two 32 KiB FP32 chunks, too few bytes in flight to keep HBM busy; the producer
+// therefore also issues TMA prefetches into L2 eight chunks ahead of its loads, across pass and tile
+// boundaries, and the loads themselves find their data in L2.
 // The arithmetic is that of the general kernel (rgb200_mma.cuh) and of the split pre-pass
 // (rgb200_prepass.cuh); only where the digits of A live differs.  Reference counterparts:
 // quantize_kmajor + gemm_wmma_i8 (repro_gemm_cuda/repro_gemm.cu:54-79, 280-364).
@@ -28,17 +28,16 @@
 
 namespace rgb200 {
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
 constexpr int RF_NT = 64;                     // columns of C per tile (one tile covers all of N)
 constexpr int RF_A_STAGES = 2;                // int8 stages the MMA reads (one k block each)
-constexpr int RF_B_STAGES = 2;
+constexpr int RF_B_STAGES = 2;                // (one stage would stall the producer, which issues B's loads in chunk order)
 constexpr int RF_F_STAGES = 2;                // FP32 landing stages
-constexpr int RF_CHUNK_K = 64;                // k per FP32 chunk
+constexpr int RF_CHUNK_K = 64;                // k per FP32 chunk: 128 rows x 256 bytes
+constexpr int RF_CHUNKS_PER_BLOCK = BLOCK_K / RF_CHUNK_K;
+constexpr int RF_LANES_PER_ROW = RF_CHUNK_K / 4;          // one 16-byte load per lane
+constexpr int RF_ROWS_PER_LOAD = 32 / RF_LANES_PER_ROW;   // rows a warp-wide load covers
+constexpr int RF_ROW_ITERS = 8 / RF_ROWS_PER_LOAD;        // loads per warp and chunk (a warp owns eight rows)
+constexpr int RF_PREFETCH = 8;                // chunks requested into L2 ahead of the loads (8 x 32 KiB per SM)
 constexpr int RF_F_STAGE_BYTES = BLOCK_M * RF_CHUNK_K * 4;
 constexpr int RF_WORK_WARPS = 16;             // converter + epilogue warps
 constexpr int RF_WORK_THREADS = RF_WORK_WARPS * 32;
@@ -58,6 +57,7 @@ struct RowFusedTraits {
     static constexpr int SMEM_BYTES = RF_F_STAGES * RF_F_STAGE_BYTES + RF_A_STAGES * A_STAGE_BYTES + RF_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
                                       RF_WORK_WARPS * CPT * 4 /* column exponents */ + BLOCK_M * 4 /* row exponents */;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    static_assert(RF_CHUNK_K == 32 || RF_CHUNK_K == 64, "a chunk row is one or two 128-byte lines");
 };
 
 struct RowFusedParams {
@@ -138,29 +138,37 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 ++f_it;
                 return true;
             };
-            // chunk order (the work warps consume in the same order): pass 1 of the CTA's first tile; then, per tile,
-            // for every half k block its pass-2 chunk followed by the same chunk of the NEXT tile for that tile's
-            // pass 1, so that the next tile's HBM reads overlap this tile's conversion work
-            if ((int)blockIdx.x < total_tiles) {
-                const int batch = blockIdx.x / P.m_tiles, m_blk = blockIdx.x - batch * P.m_tiles;
-                for (int c = 0; ok && c < 2 * P.k_blocks; ++c) ok = load_chunk(c, m_blk, batch);
-            }
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
-                const int next = tile + gridDim.x;
-                const bool has_next = next < total_tiles;
-                const int n_batch = has_next ? next / P.m_tiles : 0, n_blk = has_next ? next - n_batch * P.m_tiles : 0;
-                for (int kb = 0; ok && kb < P.k_blocks; ++kb) {
+            // Chunk order (the work warps consume in the same order): per tile all chunks for pass 1, then all chunks
+            // again for pass 2, with B's planes of a k block in front of that block's chunks.  A second cursor
+            // runs RF_PREFETCH chunks ahead of the loads and only asks for the chunk to be brought into L2, so that
+            // enough bytes are on their way from HBM although just RF_F_STAGES chunks fit shared memory.
+            struct Cursor { int tile, pass, c, batch, m_blk; };
+            const int chunks = RF_CHUNKS_PER_BLOCK * P.k_blocks;
+            auto place = [&](Cursor& x) { x.batch = x.tile / P.m_tiles; x.m_blk = x.tile - x.batch * P.m_tiles; };
+            auto step = [&](Cursor& x) {
+                if (++x.c == chunks) { x.c = 0; if (++x.pass == 2) { x.pass = 0; x.tile += gridDim.x; place(x); } }
+            };
+            auto prefetch = [&](const Cursor& x) {
+                if (x.tile >= total_tiles) return;
+                asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                             ::"l"(&tmap_a), "r"(x.c * RF_CHUNK_K), "r"(x.m_blk * BLOCK_M), "r"(x.batch) : "memory");
+            };
+            Cursor cur{(int)blockIdx.x, 0, 0, 0, 0}, ahead{(int)blockIdx.x, 0, 0, 0, 0};
+            place(cur);
+            place(ahead);
+            for (int i = 0; i < RF_PREFETCH; ++i) { prefetch(ahead); step(ahead); }
+            while (ok && cur.tile < total_tiles) {
+                if (cur.pass == 1 && cur.c % RF_CHUNKS_PER_BLOCK == 0) {         // B's planes of this k block
                     const int s = b_it % RF_B_STAGES;
                     if (!(ok = mbar_wait(b_empty(s), ((b_it / RF_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                     mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
-                    tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), kb * BLOCK_K, 0, 0, batch);
+                    tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), (cur.c / RF_CHUNKS_PER_BLOCK) * BLOCK_K, 0, 0, cur.batch);
                     ++b_it;
-                    for (int h = 0; ok && h < 2; ++h) {
-                        ok = load_chunk(2 * kb + h, m_blk, batch);
-                        if (ok && has_next) ok = load_chunk(2 * kb + h, n_blk, n_batch);
-                    }
                 }
+                if (!(ok = load_chunk(cur.c, cur.m_blk, cur.batch))) break;
+                prefetch(ahead);
+                step(ahead);
+                step(cur);
             }
             if (!ok) {
                 // abort: let copies that are still in flight land before the CTA gives up its shared memory
@@ -219,70 +227,72 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const int quarter = warp & 3;                  // TMEM lanes this warp may read
         const int cgroup = cw >> 2;                    // which sixteen columns of the tile
         int* eb_s = eb_slots + cw * CPT;
-        // Chunk layout in shared memory: [128 rows][64 k] FP32, 256 bytes per row.  A warp owns eight rows; one
-        // 16-byte load per lane covers two rows at a time (16 lanes each), rows i and i + 4 of the eight, so that
-        // the swizzled digit stores of the two half-warps fall into different bank groups.
-        const int c16 = lane & 15;                     // which four k of the chunk's 64
-        const int rsel = lane >> 4;
+        // Chunk layout in shared memory: [128 rows][RF_CHUNK_K] FP32.  A warp owns eight rows; one 16-byte load per
+        // lane covers RF_ROWS_PER_LOAD rows at a time: rows rsel * RF_ROW_ITERS + i of the eight, which makes the
+        // swizzled digit stores of the lane groups fall into different bank groups.
+        const int cl = lane % RF_LANES_PER_ROW;        // which four k of the chunk
+        const int rsel = lane / RF_LANES_PER_ROW;
         uint32_t f_it = 0, a_it = 0, tile_it = 0;
         bool ok = true;
         // one FP32 chunk into the running row maxima
-        auto max_chunk = [&](float (&m)[4]) {
+        auto max_chunk = [&](float (&m)[RF_ROW_ITERS]) {
             const int s = f_it % RF_F_STAGES;
-            bool got = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+            bool got = mbar_wait_relaxed(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
             got = __all_sync(0xFFFFFFFFu, got);
             if (!got) return false;
             const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = cw * 8 + i + 4 * rsel;
-                m[i] = abs4max(m[i], *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + c16 * 16));
+            for (int i = 0; i < RF_ROW_ITERS; ++i) {
+                const int r = cw * 8 + rsel * RF_ROW_ITERS + i;
+                m[i] = abs4max(m[i], *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + cl * 16));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(f_empty(s));
             ++f_it;
             return true;
         };
-        float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if ((int)blockIdx.x < total_tiles)                 // pass 1 of the first tile
-            for (int c = 0; ok && c < 2 * P.k_blocks; ++c) ok = max_chunk(m);
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
             const int batch = tile / P.m_tiles, m_blk = tile - batch * P.m_tiles;
-            const bool has_next = tile + (int)gridDim.x < total_tiles;
-            int e[4];
-            float f1[4];
+            // pass 1: row maxima
+            float m[RF_ROW_ITERS];
+#pragma unroll
+            for (int i = 0; i < RF_ROW_ITERS; ++i) m[i] = 0.0f;
+            for (int c = 0; ok && c < RF_CHUNKS_PER_BLOCK * P.k_blocks; ++c) ok = max_chunk(m);
+            if (!ok) break;
+            int e[RF_ROW_ITERS];
+            float f1[RF_ROW_ITERS];
             bool all_plain = true;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < RF_ROW_ITERS; ++i) {
 #pragma unroll
-                for (int o = 8; o > 0; o >>= 1) m[i] = fmaxf(m[i], __shfl_xor_sync(0xFFFFFFFFu, m[i], o));   // over the row's 16 lanes
+                for (int o = RF_LANES_PER_ROW / 2; o > 0; o >>= 1) m[i] = fmaxf(m[i], __shfl_xor_sync(0xFFFFFFFFu, m[i], o));   // over the row's lanes
                 e[i] = scale_exponent(m[i]);
                 f1[i] = quant_scale(e[i], S).f1;
                 all_plain = all_plain && plain_row(e[i]);
-                if (c16 == 0) ea_rows[cw * 8 + i + 4 * rsel] = e[i];    // the previous tile's epilogue has finished reading (done_bar)
-                m[i] = 0.0f;                                            // now collects the next tile's maxima
+                if (cl == 0) ea_rows[cw * 8 + rsel * RF_ROW_ITERS + i] = e[i];    // the previous tile's epilogue has finished reading (done_bar)
             }
             all_plain = __all_sync(0xFFFFFFFFu, all_plain);
-            // pass 2: digits into the swizzled stages, interleaved chunk by chunk with pass 1 of the next tile
+            // pass 2: digits into the swizzled stages
             for (int kb = 0; kb < P.k_blocks; ++kb, ++a_it) {
                 const int sa_i = a_it % RF_A_STAGES;
-                ok = mbar_wait(a_empty(sa_i), ((a_it / RF_A_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY);
+                ok = mbar_wait_relaxed(a_empty(sa_i), ((a_it / RF_A_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 uint8_t* stage = gen_a + sa_i * Tr::A_STAGE_BYTES;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                for (int h = 0; h < RF_CHUNKS_PER_BLOCK; ++h) {
                     const int s = f_it % RF_F_STAGES;
-                    ok = mbar_wait(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+                    ok = mbar_wait_relaxed(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
                     ok = __all_sync(0xFFFFFFFFu, ok);
                     if (!ok) break;
                     const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = cw * 8 + i + 4 * rsel;                      // row inside the tile
-                        const float4 v = *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + c16 * 16);
-                        // 128-byte rows of int8, 16-byte chunks XOR-ed with the row index modulo 8: the 128-byte swizzle
-                        const size_t off = (size_t)r * 128 + (size_t)((((4 * h + (c16 >> 2)) ^ (r & 7))) << 4) + ((c16 & 3) << 2);
+                    for (int i = 0; i < RF_ROW_ITERS; ++i) {
+                        const int r = cw * 8 + rsel * RF_ROW_ITERS + i;           // row inside the tile
+                        const float4 v = *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + cl * 16);
+                        // 128-byte rows of int8, 16-byte pieces XOR-ed with the row index modulo 8 (the 128-byte swizzle);
+                        // this chunk's k are bytes RF_CHUNK_K * h .. of the row
+                        const size_t off = (size_t)r * 128 + (size_t)((((h * (RF_CHUNK_K / 16) + (cl >> 2)) ^ (r & 7))) << 4) + ((cl & 3) << 2);
                         if (all_plain) {
                             QuantScale q; q.f1 = f1[i]; q.f2 = 1.0f; q.lim = 0;
                             store_quad_impl<S, true>(v, q, reinterpret_cast<int8_t*>(stage), Tr::A_PLANE_BYTES, off);
@@ -293,7 +303,6 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     __syncwarp();
                     if (lane == 0) mbar_arrive(f_empty(s));
                     ++f_it;
-                    if (has_next && !(ok = max_chunk(m))) break;
                 }
                 if (!ok) break;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> visible to the MMA's reads
@@ -304,7 +313,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             // every warp's row exponents are in ea_rows before any warp's epilogue reads them
             __syncwarp();
             if (lane == 0) mbar_arrive(rows_bar);
-            ok = mbar_wait(rows_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+            ok = mbar_wait_relaxed(rows_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             // epilogue: 32 rows x 16 columns per warp
@@ -315,7 +324,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             if (lane < CPT) eb_s[lane] = col0 + lane < P.N ? __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane) : 0;
             __syncwarp();
             const int ea = ea_rows[row_in_tile];
-            ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = mbar_wait_relaxed(tmem_full_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -368,7 +377,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             // ea_rows is rewritten by the next tile's first pass
             __syncwarp();
             if (lane == 0) mbar_arrive(done_bar);
-            ok = mbar_wait(done_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = mbar_wait_relaxed(done_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
         }
     }

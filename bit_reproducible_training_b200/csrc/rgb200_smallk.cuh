@@ -8,9 +8,11 @@
 //   * 128 x 48 tiles: the (2S-1) * 48 accumulator columns fit TMEM twice.  Two groups of eight
 //     epilogue warps own one accumulator set each and alternate tiles, so sixteen warps drain, round
 //     and store while the MMA warp is already one or two tiles ahead.
-//   * few, wide MMAs: the single issuing thread needs on the order of a hundred cycles per MMA whatever its
-//     size, so a tile's first k step takes 2S-1 MMAs (see issue_first_k_step) instead of S^2, and the
-//     48-column tile spreads that cost over half as many more outputs than a 32-column one would.
+//   * issue cost: a thread needs on the order of a hundred cycles to issue an MMA whatever its size (a chain
+//     of dependent instructions on a scheduler it shares with epilogue warps), far more than these small MMAs
+//     keep the tensor pipe busy.  So a tile's first k step takes 2S-1 MMAs (see issue_first_k_step) instead of
+//     S^2, descriptors are formed with one addition (umma_i8_lo), the 48-column tile spreads the cost over half
+//     as many more outputs than a 32-column one would, and two threads on two schedulers issue alternate tiles.
 //   * A-stationary: a CTA walks a contiguous range of tiles with the column tile running fastest, so
 //     the 128-row A tile (all S planes, the whole K) is loaded once per row of tiles into one of two
 //     buffers; only the small B tiles stream through a ring of stages.
@@ -28,7 +30,10 @@ constexpr int SK_B_STAGES = 5;
 constexpr int SK_EPI_GROUPS = 2;              // one per accumulator set
 constexpr int SK_GROUP_WARPS = 8;
 constexpr int SK_GROUP_THREADS = SK_GROUP_WARPS * 32;
-constexpr int SK_THREADS = 64 + SK_EPI_GROUPS * SK_GROUP_THREADS;    // 576
+// warp 0: TMA producer; warp 1 and the last warp: the MMA issuers of accumulator set 0 and 1; between them the
+// sixteen epilogue warps
+constexpr int SK_THREADS = 64 + SK_EPI_GROUPS * SK_GROUP_THREADS + 32;    // 608
+constexpr int SK_SECOND_ISSUER_WARP = SK_THREADS / 32 - 1;
 
 // 32 lanes x 8 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
@@ -37,21 +42,85 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
                  : "r"(taddr) : "memory");
 }
 
+// Bounded wait for the many-thread roles (epilogue, converters): like mbar_wait, but a waiting thread sleeps a little
+// between polls, so that the issue slots of its scheduler go to the single thread that feeds the tensor pipe.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    for (uint32_t spins = 1;; ++spins) {
+        __nanosleep(40);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CLOCKS) {
+                atomicCAS(status, 0, code);
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+
+// Position in the (batch, row tile, column tile) order, column tile fastest, advanced without divisions (the roles
+// that walk it are single threads on the critical path).
+struct TileWalk {
+    int n_blk, m_blk, batch;
+    __device__ __forceinline__ void init(long long t, int n_tiles, int m_tiles) {
+        const long long group = t / n_tiles;
+        n_blk = (int)(t - group * n_tiles);
+        batch = (int)(group / m_tiles);
+        m_blk = (int)(group - (long long)batch * m_tiles);
+    }
+    // Moves `step` tiles on; true when that entered another row of tiles (another A tile).
+    __device__ __forceinline__ bool advance(int step, int n_tiles, int m_tiles) {
+        n_blk += step;
+        bool wrapped = false;
+        while (n_blk >= n_tiles) {
+            n_blk -= n_tiles;
+            wrapped = true;
+            if (++m_blk == m_tiles) { m_blk = 0; ++batch; }
+        }
+        return wrapped;
+    }
+};
+
 // Exact sum T = sum_L level_L * 128^(2S-2-L) for level sums over at most 128 values of k.  Each level is then
 // below 128 * 20352 < 2^22, so neighbouring levels combine in 32-bit arithmetic (level * 128 stays below 2^29)
 // and only the last steps need 64 bits.
+__device__ __forceinline__ long long mad_wide(int a, int b, long long c) {      // a * b + c with a 32 x 32 -> 64 bit product
+    long long d;
+    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+    return d;
+}
 template <int S>
 __device__ __forceinline__ typename std::conditional<S == 1, int, long long>::type
 combine_levels_short_k(const int (&lv)[2 * S - 1][8], int j) {
     if constexpr (S == 1) {
         return lv[0][j];
     } else if constexpr (S == 2) {
-        return (long long)(lv[2][j] + lv[1][j] * 128) + (long long)lv[0][j] * 16384;
+        return mad_wide(lv[0][j], 1 << 14, (long long)(lv[2][j] + lv[1][j] * 128));
     } else {
         const int low = lv[4][j] + lv[3][j] * 128;
         const int mid = lv[2][j] + lv[1][j] * 128;
-        return (long long)low + (long long)mid * 16384 + (long long)lv[0][j] * 268435456ll;
+        return mad_wide(lv[0][j], 1 << 28, mad_wide(mid, 1 << 14, (long long)low));
     }
+}
+
+// The 64-bit shared-memory matrix descriptor of smem_desc_sw128 in two halves: the upper word is a constant, and
+// the lower word of an operand at a byte offset (a multiple of 16) is the base's lower word plus offset / 16, so
+// the issuing thread - whose instruction latency is what bounds a short-K tile - spends one addition per operand.
+constexpr uint32_t SW128_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t sw128_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_i8_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "n"(ACCUMULATE ? 1 : 0), "r"(SW128_DESC_HI) : "memory");
 }
 
 // First k step of a tile: level L = p + q is written for the first time by (p = 0, q = L) or, for L >= S, by
@@ -62,12 +131,13 @@ combine_levels_short_k(const int (&lv)[2 * S - 1][8], int j) {
 template <int S, int NT>
 __device__ __forceinline__ void issue_first_k_step(uint32_t acc, uint32_t sa, uint32_t sb, uint32_t a_plane_bytes,
                                                    uint32_t b_plane_bytes) {
-    umma_i8(acc, smem_desc_sw128(sa), smem_desc_sw128(sb), idesc_i8(BLOCK_M, S * NT), 0u);
+    const uint32_t a_lo = sw128_desc_lo(sa), b_lo = sw128_desc_lo(sb);
+    umma_i8_lo<false>(acc, a_lo, b_lo, idesc_i8(BLOCK_M, S * NT));
 #pragma unroll
     for (int p = 1; p < S; ++p) {
-        umma_i8(acc + p * NT, smem_desc_sw128(sa + p * a_plane_bytes), smem_desc_sw128(sb), idesc_i8(BLOCK_M, (S - 1) * NT), 1u);
-        umma_i8(acc + (p + S - 1) * NT, smem_desc_sw128(sa + p * a_plane_bytes), smem_desc_sw128(sb + (S - 1) * b_plane_bytes),
-                idesc_i8(BLOCK_M, NT), 0u);
+        umma_i8_lo<true>(acc + p * NT, a_lo + p * (a_plane_bytes >> 4), b_lo, idesc_i8(BLOCK_M, (S - 1) * NT));
+        umma_i8_lo<false>(acc + (p + S - 1) * NT, a_lo + p * (a_plane_bytes >> 4), b_lo + (S - 1) * (b_plane_bytes >> 4),
+                          idesc_i8(BLOCK_M, NT));
     }
 }
 
@@ -130,7 +200,7 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const long long t0 = total * blockIdx.x / gridDim.x, t1 = total * (blockIdx.x + 1) / gridDim.x;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), SK_EPI_GROUPS); }
         for (int s = 0; s < SK_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
         for (int g = 0; g < SK_EPI_GROUPS; ++g) { mbar_init(tmem_full(g), 1); mbar_init(tmem_empty(g), SK_GROUP_THREADS); }
         *abort_flag = 0;
@@ -147,24 +217,23 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             uint32_t a_it = 0, b_it = 0;
-            long long prev_group = -1;
-            bool ok = true;
-            for (long long t = t0; t < t1; ++t, ++b_it) {
-                const long long group = t / P.n_tiles;
-                const int n_blk = (int)(t - group * P.n_tiles);
-                const int batch = (int)(group / P.m_tiles), m_blk = (int)(group - (long long)batch * P.m_tiles);
-                if (group != prev_group) {
+            bool ok = true, new_row = true;
+            TileWalk w;
+            w.init(t0, P.n_tiles, P.m_tiles);
+            const int count = (int)(t1 - t0);
+            for (int i = 0; i < count; ++i, ++b_it) {
+                if (new_row) {
                     const int ab = a_it & 1;
                     if (!(ok = mbar_wait(a_empty(ab), ((a_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                     mbar_arrive_expect_tx(a_full(ab), Tr::A_BYTES);
-                    tma_load_4d(a_base + ab * Tr::A_BYTES, &tmap_a, a_full(ab), 0, m_blk * BLOCK_M, 0, batch);
+                    tma_load_4d(a_base + ab * Tr::A_BYTES, &tmap_a, a_full(ab), 0, w.m_blk * BLOCK_M, 0, w.batch);
                     ++a_it;
-                    prev_group = group;
                 }
                 const int s = b_it % SK_B_STAGES;
                 if (!(ok = mbar_wait(b_empty(s), ((b_it / SK_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                 mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
-                tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), 0, n_blk * NT, 0, batch);
+                tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), 0, w.n_blk * NT, 0, w.batch);
+                new_row = w.advance(1, P.n_tiles, P.m_tiles);
             }
             if (!ok) {
                 // abort: let copies that are still in flight land before the CTA gives up its shared memory
@@ -183,40 +252,49 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || warp == SK_SECOND_ISSUER_WARP) {
+        // ---------------------------------------------------------------- MMA issuers
+        // One thread per accumulator set: issuer g takes the tiles of parity g.  A tile's MMAs cost the issuing thread
+        // far more time than they cost the tensor pipe, so two threads on two schedulers issue alternate tiles.
+        // Both follow the rows of tiles: each waits for a row's A tile and, after its last tile of the row, commits
+        // to the A buffer's "empty" barrier (two arrivals: tcgen05.commit covers the committing thread's MMAs only).
         if (lane == 0) {
             constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
-            uint32_t a_it = 0, b_it = 0;
-            long long prev_group = -1;
+            const int g = warp == 1 ? 0 : 1;
+            uint32_t a_it = 0, use = 0;
             uint32_t sa = 0, cur_ab = 0;
-            bool ok = true;
-            for (long long t = t0; ok && t < t1; ++t, ++b_it) {
-                const long long group = t / P.n_tiles;
-                if (group != prev_group) {
+            bool ok = true, new_row = true;
+            int n_blk = (int)(t0 % P.n_tiles);
+            const int count = (int)(t1 - t0);
+            for (int i = 0; ok && i < count; ++i) {
+                if (new_row) {
                     cur_ab = a_it & 1;
                     if (!(ok = mbar_wait(a_full(cur_ab), (a_it >> 1) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
                     sa = a_base + cur_ab * Tr::A_BYTES;
                     ++a_it;
-                    prev_group = group;
                 }
-                const int s = b_it % SK_B_STAGES;
-                if (!(ok = mbar_wait(b_full(s), (b_it / SK_B_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
-                const int g = b_it & 1;                 // accumulator set = tile parity
-                if (!(ok = mbar_wait(tmem_empty(g), ((b_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
-                tc_fence_after();
-                const uint32_t sb = b_base + s * Tr::B_STAGE_BYTES;
-                const uint32_t acc = tmem_base + g * Tr::ACC_COLS;
-                issue_first_k_step<S, NT>(acc, sa, sb, Tr::A_PLANE_BYTES, Tr::B_PLANE_BYTES);
-                for (int k = 1; k < P.k_steps; ++k)
+                if ((i & 1) == g) {
+                    const int s = i % SK_B_STAGES;
+                    if (!(ok = mbar_wait(b_full(s), (i / SK_B_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                    if (!(ok = mbar_wait(tmem_empty(g), (use & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_TMEM_EMPTY))) break;
+                    ++use;
+                    tc_fence_after();
+                    const uint32_t sb = b_base + s * Tr::B_STAGE_BYTES;
+                    const uint32_t acc = tmem_base + g * Tr::ACC_COLS;
+                    issue_first_k_step<S, NT>(acc, sa, sb, Tr::A_PLANE_BYTES, Tr::B_PLANE_BYTES);
+                    const uint32_t a_lo = sw128_desc_lo(sa), b_lo = sw128_desc_lo(sb);
+                    for (int k = 1; k < P.k_steps; ++k)
 #pragma unroll
-                    for (int p = 0; p < S; ++p)
-                        umma_i8(acc + p * NT, smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES + k * UMMA_K),
-                                smem_desc_sw128(sb + k * UMMA_K), IDESC_WIDE, 1u);
-                umma_commit(b_empty(s));
-                umma_commit(tmem_full(g));
-                // last tile of this row of tiles (or of the CTA's range): the A buffer may be refilled
-                if (t + 1 == t1 || (t + 1) / P.n_tiles != group) umma_commit(a_empty(cur_ab));
+                        for (int p = 0; p < S; ++p)
+                            umma_i8_lo<true>(acc + p * NT, a_lo + p * (Tr::A_PLANE_BYTES >> 4) + k * (UMMA_K >> 4),
+                                             b_lo + k * (UMMA_K >> 4), IDESC_WIDE);
+                    umma_commit(b_empty(s));
+                    umma_commit(tmem_full(g));
+                }
+                // last tile of this row of tiles (or of the CTA's range): this issuer is done with the A buffer
+                new_row = ++n_blk == P.n_tiles;
+                if (new_row) n_blk = 0;
+                if (new_row || i + 1 == count) umma_commit(a_empty(cur_ab));
             }
         }
     } else {
@@ -230,18 +308,34 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         int* eb_s = eb_slots + ew * CPT;
         bool ok = true;
         uint32_t use = 0;                              // how often this group's accumulator set has been used
-        for (long long t = t0 + g; ok && t < t1; t += SK_EPI_GROUPS, ++use) {
-            const long long group = t / P.n_tiles;
-            const int n_blk = (int)(t - group * P.n_tiles);
-            const int batch = (int)(group / P.m_tiles), m_blk = (int)(group - (long long)batch * P.m_tiles);
+        TileWalk w;
+        w.init(t0 + g, P.n_tiles, P.m_tiles);
+        const int count = (int)(t1 - t0);
+        for (int i = g; ok && i < count; i += SK_EPI_GROUPS, ++use, w.advance(SK_EPI_GROUPS, P.n_tiles, P.m_tiles)) {
+            const int n_blk = w.n_blk, m_blk = w.m_blk, batch = w.batch;
             const int row = m_blk * BLOCK_M + row_in_tile;
             const bool row_ok = row < P.M;
             const int ea = row_ok ? __ldg(P.expo_a + (size_t)batch * P.M + row) : 0;
             const int col0 = n_blk * NT + half * CPT;
+            // The slot holds the column exponents already shifted into the exponent field of a float, and the warp
+            // learns their range: when every exponent this row can meet keeps any non-zero sum a normal number
+            // (the float of a non-zero sum has a biased exponent of 127..190, so E in [-126, 64] is safe), the
+            // rounding below needs no range check per output.
             __syncwarp();
-            if (lane < CPT) eb_s[lane] = col0 + lane < P.N ? __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane) : 0;
-            __syncwarp();
-            ok = mbar_wait(tmem_full(g), use & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            int eb_lo = 0x7FFFFFFF, eb_hi = -0x7FFFFFFF;
+            if (lane < CPT && col0 + lane < P.N) {
+                const int eb = __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane);
+                eb_s[lane] = eb << 23;
+                eb_lo = eb_hi = eb;
+            } else if (lane < CPT) {
+                eb_s[lane] = 0;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                eb_lo = min(eb_lo, __shfl_xor_sync(0xFFFFFFFFu, eb_lo, o));
+                eb_hi = max(eb_hi, __shfl_xor_sync(0xFFFFFFFFu, eb_hi, o));
+            }
+            ok = mbar_wait_relaxed(tmem_full(g), use & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -263,17 +357,20 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             // one rounding per output
             uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
             const int ebase = ea + P.e0;
+            const bool safe = ebase + eb_lo >= -126 && ebase + eb_hi <= 64;
+            const uint32_t ebase23 = (uint32_t)ebase << 23;
             auto round4 = [&](int j, uint32_t (&r)[4]) {
-                bool k0, k1, k2, k3;
-                r[0] = round_to_f32_bits_signed(T[j + 0], ebase + eb_s[j + 0], &k0);
-                r[1] = round_to_f32_bits_signed(T[j + 1], ebase + eb_s[j + 1], &k1);
-                r[2] = round_to_f32_bits_signed(T[j + 2], ebase + eb_s[j + 2], &k2);
-                r[3] = round_to_f32_bits_signed(T[j + 3], ebase + eb_s[j + 3], &k3);
-                if (!(k0 && k1 && k2 && k3)) {          // zero, subnormal or overflowing results: exact path
-                    r[0] = round_to_f32_bits(T[j + 0], ebase + eb_s[j + 0]);
-                    r[1] = round_to_f32_bits(T[j + 1], ebase + eb_s[j + 1]);
-                    r[2] = round_to_f32_bits(T[j + 2], ebase + eb_s[j + 2]);
-                    r[3] = round_to_f32_bits(T[j + 3], ebase + eb_s[j + 3]);
+                if (safe) {
+                    // one hardware conversion (round to nearest even, sign included), then the exponent is added in
+                    // place; a zero sum converts to +0 and stays +0
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t fb = f32_bits(__ll2float_rn((long long)T[j + q]));
+                        r[q] = fb ? fb + ebase23 + (uint32_t)eb_s[j + q] : 0u;
+                    }
+                } else {                                // subnormal or overflowing results are possible: exact path
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) r[q] = round_to_f32_bits(T[j + q], ebase + (eb_s[j + q] >> 23));
                 }
             };
             const bool whole = col0 + CPT <= P.N;

@@ -216,7 +216,7 @@ class HostGemm:
     is still on its way.  Row blocks are independent products, so the bits equal those of one call.
     Device buffers, workspace, streams and events are created once; a call allocates nothing."""
 
-    def __init__(self, M, N, K, cfg=None, block_rows=512, device=None):
+    def __init__(self, M, N, K, cfg=None, block_rows=0, device=None):
         self.M, self.N, self.K, self.cfg = M, N, K, cfg or Config()
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self._h = C.c_void_p()

@@ -134,7 +134,7 @@ int rgb200_gemm_partial_scatter_ws(const float* A, const float* B, const float* 
  * and the copy of the finished rows of C back to the host overlap the transfer of the next block.
  * Row blocks are independent products, so the result has the bits of a single call.
  *   rgb200_host_gemm_create   allocates the device copies of A, B, C, the workspace, three streams and the
- *                             events for one (M, N, K, cfg) on the current device; block_rows <= 0 picks 512.
+ *                             events for one (M, N, K, cfg) on the current device; block_rows <= 0 picks 256.
  *   rgb200_gemm_fp32_host     enqueues one product; allocates nothing and does not synchronise.  Work starts
  *                             after what is already enqueued on `stream`, and `stream` continues after the
  *                             last byte of C has landed: synchronise it (or record an event on it) before

@@ -256,7 +256,7 @@ def test_host_buffer_pipeline_matches_single_call():
     hBt = torch.from_numpy(np.ascontiguousarray(B.reshape(K, N).T).reshape(-1)).pin_memory()
     for cfg, a, b in ((rg.Config(trans_a=True), hAt, hB), (rg.Config(trans_a=True, trans_b=True), hAt, hBt),
                       (rg.Config(trans_b=True), hA, hBt)):
-        pipe = rg.HostGemm(M, N, K, cfg)
+        pipe = rg.HostGemm(M, N, K, cfg, block_rows=512)
         hC.fill_(float("nan"))
         pipe(a, b, hC)
         torch.cuda.synchronize()
