@@ -791,35 +791,25 @@ cudaError_t conv_run(ConvKind kind, const float* p, const float* q, float* out, 
     const DeviceInfo* dev = nullptr;
     if ((e = check_device(L.algo, &dev)) != cudaSuccess) return e;
     // The smallest layers (a LeNet-style first convolution) skip the tensor cores: one thread per output
-    // evaluates the definition directly (rgb200_conv_direct.cuh).  Scratch - the fixed-point weights and the
-    // exponents - sits where the implicit-GEMM path would put A's digit planes.
+    // evaluates the definition directly (rgb200_conv_direct.cuh); one launch, no workspace traffic.
     {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
-        int* scratch = reinterpret_cast<int*>(static_cast<char*>(ws) + L.qa);
-        const size_t room = L.total - L.qa;
         const long long weights = (long long)g.F * g.K;
-        if (kind == CONV_FORWARD && g.K <= CONV_DIRECT_MAX_K && g.F <= CONV_DIRECT_MAX_F &&
-            room >= (size_t)(weights + g.F) * sizeof(int)) {
-            int* wq = scratch;
-            int* ef = scratch + weights;
+        if (kind == CONV_FORWARD && g.K <= CONV_DIRECT_MAX_K && g.F <= CONV_DIRECT_MAX_F) {
             const long long windows = (long long)g.N * g.OH * g.OW;
-            #define RGB_CONV_FWD(SS) do { \
-                conv_direct_filters_kernel<SS><<<1, 32 * g.F, 0, st>>>(q, wq, ef, g.F, g.K); \
-                conv_direct_forward_kernel<SS><<<(unsigned)((windows + CONV_DIRECT_THREADS - 1) / CONV_DIRECT_THREADS), CONV_DIRECT_THREADS, 0, st>>>(p, wq, ef, out, g); } while (0)
-            if (S == 1) RGB_CONV_FWD(1); else if (S == 2) RGB_CONV_FWD(2); else RGB_CONV_FWD(3);
-            #undef RGB_CONV_FWD
+            const unsigned grid = (unsigned)((windows + CONV_DIRECT_THREADS - 1) / CONV_DIRECT_THREADS);
+            if (S == 1) conv_direct_forward_kernel<1><<<grid, CONV_DIRECT_THREADS, 0, st>>>(p, q, out, g);
+            else if (S == 2) conv_direct_forward_kernel<2><<<grid, CONV_DIRECT_THREADS, 0, st>>>(p, q, out, g);
+            else conv_direct_forward_kernel<3><<<grid, CONV_DIRECT_THREADS, 0, st>>>(p, q, out, g);
             return cudaGetLastError();
         }
+        // the per-image maximum of dY is recomputed by every CTA of the image: worth it only for small images
         if (kind == CONV_GRAD_INPUT && weights <= CONV_DIRECT_MAX_WEIGHTS && (long long)g.F * g.KH * g.KW <= 256 &&
-            room >= (size_t)(weights + g.N + 1) * sizeof(int)) {
-            int* wq = scratch;
-            int* e_img = scratch + weights;
-            const long long pixels = (long long)g.N * g.C * g.H * g.W;
-            #define RGB_CONV_DX(SS) do { \
-                conv_direct_grad_input_scales_kernel<SS><<<g.N + 1, 256, 0, st>>>(p, q, e_img, wq, g.N, g.F * g.OH * g.OW, (int)weights); \
-                conv_direct_grad_input_kernel<SS><<<(unsigned)((pixels + CONV_DIRECT_THREADS - 1) / CONV_DIRECT_THREADS), CONV_DIRECT_THREADS, 0, st>>>(p, wq, e_img, out, g); } while (0)
-            if (S == 1) RGB_CONV_DX(1); else if (S == 2) RGB_CONV_DX(2); else RGB_CONV_DX(3);
-            #undef RGB_CONV_DX
+            (long long)g.F * g.OH * g.OW <= 16384) {
+            const dim3 grid((unsigned)((g.C * g.H * g.W + CONV_DIRECT_THREADS - 1) / CONV_DIRECT_THREADS), (unsigned)g.N);
+            if (S == 1) conv_direct_grad_input_kernel<1><<<grid, CONV_DIRECT_THREADS, 0, st>>>(p, q, out, g);
+            else if (S == 2) conv_direct_grad_input_kernel<2><<<grid, CONV_DIRECT_THREADS, 0, st>>>(p, q, out, g);
+            else conv_direct_grad_input_kernel<3><<<grid, CONV_DIRECT_THREADS, 0, st>>>(p, q, out, g);
             return cudaGetLastError();
         }
     }

@@ -201,6 +201,41 @@ __host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
     return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// The 64-bit shared-memory matrix descriptor of smem_desc_sw128 in two halves: the upper word is a constant, and
+// the lower word of an operand at a byte offset (a multiple of 16) is the base's lower word plus offset / 16, so
+// the issuing thread - a single thread whose instruction latency competes with the tensor pipe's time per MMA - spends one
+// addition per operand.
+constexpr uint32_t SW128_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t sw128_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_i8_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "n"(ACCUMULATE ? 1 : 0), "r"(SW128_DESC_HI) : "memory");
+}
+
+// First k step of a tile: level L = p + q is written for the first time by (p = 0, q = L) or, for L >= S, by
+// (p = L - S + 1, q = S - 1), and accumulated into by every other pair.  So A plane 0 takes one MMA over all S
+// planes of B that overwrites levels 0..S-1, and every further A plane p one MMA over B planes 0..S-2 that
+// accumulates into levels p..p+S-2 plus one over B plane S-1 that overwrites the new level p+S-1:
+// 2S-1 MMAs.  sa / sb: shared-memory addresses of the operands' plane 0 at this k step.
+template <int S, int NT>
+__device__ __forceinline__ void issue_first_k_step(uint32_t acc, uint32_t sa, uint32_t sb, uint32_t a_plane_bytes,
+                                                   uint32_t b_plane_bytes) {
+    const uint32_t a_lo = sw128_desc_lo(sa), b_lo = sw128_desc_lo(sb);
+    umma_i8_lo<false>(acc, a_lo, b_lo, idesc_i8(BLOCK_M, S * NT));
+#pragma unroll
+    for (int p = 1; p < S; ++p) {
+        umma_i8_lo<true>(acc + p * NT, a_lo + p * (a_plane_bytes >> 4), b_lo, idesc_i8(BLOCK_M, (S - 1) * NT));
+        umma_i8_lo<false>(acc + (p + S - 1) * NT, a_lo + p * (a_plane_bytes >> 4), b_lo + (S - 1) * (b_plane_bytes >> 4),
+                          idesc_i8(BLOCK_M, NT));
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Tile schedule shared by the three roles.  Order: batch-major, then K range, then groups of 16
 // row tiles swept column tile by column tile, so CTAs running together share operand panels in L2.
@@ -356,7 +391,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t IDESC_WIDE = idesc_i8(BLOCK_M, S * NT);
-            constexpr uint32_t IDESC_ONE = idesc_i8(BLOCK_M, NT);
             uint32_t it = 0, tile_it = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
@@ -370,25 +404,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * Tr::STAGE_BYTES;
                     const uint32_t sb = sa + Tr::A_STAGE_BYTES;
+                    const uint32_t a_lo = sw128_desc_lo(sa), b_lo = sw128_desc_lo(sb);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         if (kb == tc.kb_begin && k == 0) {
-                            // first k step of the tile: every level block needs its own overwrite flag
-#pragma unroll
-                            for (int p = 0; p < S; ++p)
-#pragma unroll
-                                for (int q = 0; q < S; ++q)
-                                    umma_i8(tmem_base + (p + q) * NT,
-                                            smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES),
-                                            smem_desc_sw128(sb + q * Tr::B_PLANE_BYTES),
-                                            IDESC_ONE, (p != 0 && q != S - 1) ? 1u : 0u);
+                            // first k step of the tile: 2S-1 MMAs that overwrite each level where it is first written
+                            issue_first_k_step<S, NT>(tmem_base, sa, sb, Tr::A_PLANE_BYTES, Tr::B_PLANE_BYTES);
                         } else {
 #pragma unroll
                             for (int p = 0; p < S; ++p)
-                                umma_i8(tmem_base + p * NT,
-                                        smem_desc_sw128(sa + p * Tr::A_PLANE_BYTES + k * UMMA_K),
-                                        smem_desc_sw128(sb + k * UMMA_K),
-                                        IDESC_WIDE, 1u);
+                                umma_i8_lo<true>(tmem_base + p * NT, a_lo + p * (Tr::A_PLANE_BYTES >> 4) + k * (UMMA_K >> 4),
+                                                 b_lo + k * (UMMA_K >> 4), IDESC_WIDE);
                         }
                     }
                     umma_commit(empty_bar(s));          // frees the stage once these MMAs have read it

@@ -13,9 +13,9 @@
 //     keep the tensor pipe busy.  So a tile's first k step takes 2S-1 MMAs (see issue_first_k_step) instead of
 //     S^2, descriptors are formed with one addition (umma_i8_lo), the 48-column tile spreads the cost over half
 //     as many more outputs than a 32-column one would, and two threads on two schedulers issue alternate tiles.
-//   * A-stationary: a CTA walks a contiguous range of tiles with the column tile running fastest, so
-//     the 128-row A tile (all S planes, the whole K) is loaded once per row of tiles into one of two
-//     buffers; only the small B tiles stream through a ring of stages.
+//   * A-stationary: a CTA takes half rows of tiles round-robin and walks each with the column tile running
+//     fastest, so the 128-row A tile (all S planes, the whole K) is loaded once per half row into one of two
+//     buffers; only the small B tiles stream through a ring of stages (see TileWalk).
 //   * k steps beyond K (zero padding of the 128-byte block) are not issued.
 // The arithmetic (level accumulators, exact INT64 sums, single rounding) is that of the general
 // kernel; see rgb200_mma.cuh.  Reference counterpart: gemm_wmma_i8<S> (repro_gemm_cuda/repro_gemm.cu:280-364);
@@ -62,26 +62,38 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
     }
 }
 
-// Position in the (batch, row tile, column tile) order, column tile fastest, advanced without divisions (the roles
-// that walk it are single threads on the critical path).
+// The order in which a CTA visits tiles.  A "unit" is half a row of tiles (one A tile, half of the column tiles); the
+// CTAs take units round-robin, so the CTAs running together work on neighbouring rows of a few batches and their B
+// planes are shared in L2 (a contiguous range per CTA spreads the 148 CTAs over all batches at once, and with the
+// output stream passing through L2 the B tiles then keep coming from HBM).  Within a unit the column tile runs
+// fastest, so the A tile is loaded once per unit.  No 64-bit divisions: the roles that walk this order are single
+// threads on the critical path.
 struct TileWalk {
-    int n_blk, m_blk, batch;
-    __device__ __forceinline__ void init(long long t, int n_tiles, int m_tiles) {
-        const long long group = t / n_tiles;
-        n_blk = (int)(t - group * n_tiles);
-        batch = (int)(group / m_tiles);
-        m_blk = (int)(group - (long long)batch * m_tiles);
+    int unit, stride, total_units, halves, split;     // split: first column tile of the second half
+    int n_tiles, m_tiles;
+    int n_blk, n_end, m_blk, batch;
+    __device__ __forceinline__ void place() {
+        const int row = unit / halves, half = unit - row * halves;
+        batch = row / m_tiles;
+        m_blk = row - batch * m_tiles;
+        n_blk = half ? split : 0;
+        n_end = (half || halves == 1) ? n_tiles : split;
     }
-    // Moves `step` tiles on; true when that entered another row of tiles (another A tile).
-    __device__ __forceinline__ bool advance(int step, int n_tiles, int m_tiles) {
-        n_blk += step;
-        bool wrapped = false;
-        while (n_blk >= n_tiles) {
-            n_blk -= n_tiles;
-            wrapped = true;
-            if (++m_blk == m_tiles) { m_blk = 0; ++batch; }
-        }
-        return wrapped;
+    __device__ __forceinline__ void init(int first_unit, int stride_, int n_tiles_, int m_tiles_, int batches) {
+        n_tiles = n_tiles_; m_tiles = m_tiles_;
+        halves = n_tiles >= 2 ? 2 : 1;
+        split = (n_tiles + 1) / 2;
+        total_units = batches * m_tiles * halves;
+        unit = first_unit; stride = stride_;
+        if (valid()) place();
+    }
+    __device__ __forceinline__ bool valid() const { return unit < total_units; }
+    // Moves one tile on; true when that left the current unit (the next tile, if any, needs another A tile).
+    __device__ __forceinline__ bool advance() {
+        if (++n_blk < n_end) return false;
+        unit += stride;
+        if (valid()) place();
+        return true;
     }
 };
 
@@ -104,40 +116,6 @@ combine_levels_short_k(const int (&lv)[2 * S - 1][8], int j) {
         const int low = lv[4][j] + lv[3][j] * 128;
         const int mid = lv[2][j] + lv[1][j] * 128;
         return mad_wide(lv[0][j], 1 << 28, mad_wide(mid, 1 << 14, (long long)low));
-    }
-}
-
-// The 64-bit shared-memory matrix descriptor of smem_desc_sw128 in two halves: the upper word is a constant, and
-// the lower word of an operand at a byte offset (a multiple of 16) is the base's lower word plus offset / 16, so
-// the issuing thread - whose instruction latency is what bounds a short-K tile - spends one addition per operand.
-constexpr uint32_t SW128_DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t sw128_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
-template <bool ACCUMULATE>
-__device__ __forceinline__ void umma_i8_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "mov.b64 da, {%1, %5};\n\t"
-        "mov.b64 db, {%2, %5};\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "n"(ACCUMULATE ? 1 : 0), "r"(SW128_DESC_HI) : "memory");
-}
-
-// First k step of a tile: level L = p + q is written for the first time by (p = 0, q = L) or, for L >= S, by
-// (p = L - S + 1, q = S - 1), and accumulated into by every other pair.  So A plane 0 takes one MMA over all S
-// planes of B that overwrites levels 0..S-1, and every further A plane p one MMA over B planes 0..S-2 that
-// accumulates into levels p..p+S-2 plus one over B plane S-1 that overwrites the new level p+S-1:
-// 2S-1 MMAs.  sa / sb: shared-memory addresses of the operands' plane 0 at this k step.
-template <int S, int NT>
-__device__ __forceinline__ void issue_first_k_step(uint32_t acc, uint32_t sa, uint32_t sb, uint32_t a_plane_bytes,
-                                                   uint32_t b_plane_bytes) {
-    const uint32_t a_lo = sw128_desc_lo(sa), b_lo = sw128_desc_lo(sb);
-    umma_i8_lo<false>(acc, a_lo, b_lo, idesc_i8(BLOCK_M, S * NT));
-#pragma unroll
-    for (int p = 1; p < S; ++p) {
-        umma_i8_lo<true>(acc + p * NT, a_lo + p * (a_plane_bytes >> 4), b_lo, idesc_i8(BLOCK_M, (S - 1) * NT));
-        umma_i8_lo<false>(acc + (p + S - 1) * NT, a_lo + p * (a_plane_bytes >> 4), b_lo + (S - 1) * (b_plane_bytes >> 4),
-                          idesc_i8(BLOCK_M, NT));
     }
 }
 
@@ -195,9 +173,6 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int* eb_slots = reinterpret_cast<int*>(gen_bar + Tr::BAR_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // this CTA's contiguous range of tiles; flat order: batch, row tile, column tile (fastest)
-    const long long total = (long long)P.batch * P.m_tiles * P.n_tiles;
-    const long long t0 = total * blockIdx.x / gridDim.x, t1 = total * (blockIdx.x + 1) / gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), SK_EPI_GROUPS); }
@@ -219,9 +194,8 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             uint32_t a_it = 0, b_it = 0;
             bool ok = true, new_row = true;
             TileWalk w;
-            w.init(t0, P.n_tiles, P.m_tiles);
-            const int count = (int)(t1 - t0);
-            for (int i = 0; i < count; ++i, ++b_it) {
+            w.init(blockIdx.x, gridDim.x, P.n_tiles, P.m_tiles, P.batch);
+            for (; w.valid(); ++b_it) {
                 if (new_row) {
                     const int ab = a_it & 1;
                     if (!(ok = mbar_wait(a_empty(ab), ((a_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
@@ -233,7 +207,7 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (!(ok = mbar_wait(b_empty(s), ((b_it / SK_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                 mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
                 tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), 0, w.n_blk * NT, 0, w.batch);
-                new_row = w.advance(1, P.n_tiles, P.m_tiles);
+                new_row = w.advance();
             }
             if (!ok) {
                 // abort: let copies that are still in flight land before the CTA gives up its shared memory
@@ -264,9 +238,9 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             uint32_t a_it = 0, use = 0;
             uint32_t sa = 0, cur_ab = 0;
             bool ok = true, new_row = true;
-            int n_blk = (int)(t0 % P.n_tiles);
-            const int count = (int)(t1 - t0);
-            for (int i = 0; ok && i < count; ++i) {
+            TileWalk w;
+            w.init(blockIdx.x, gridDim.x, P.n_tiles, P.m_tiles, P.batch);
+            for (int i = 0; ok && w.valid(); ++i) {
                 if (new_row) {
                     cur_ab = a_it & 1;
                     if (!(ok = mbar_wait(a_full(cur_ab), (a_it >> 1) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
@@ -291,10 +265,9 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     umma_commit(b_empty(s));
                     umma_commit(tmem_full(g));
                 }
-                // last tile of this row of tiles (or of the CTA's range): this issuer is done with the A buffer
-                new_row = ++n_blk == P.n_tiles;
-                if (new_row) n_blk = 0;
-                if (new_row || i + 1 == count) umma_commit(a_empty(cur_ab));
+                // last tile of this unit: this issuer is done with the A buffer
+                new_row = w.advance();
+                if (new_row) umma_commit(a_empty(cur_ab));
             }
         }
     } else {
@@ -309,10 +282,11 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         bool ok = true;
         uint32_t use = 0;                              // how often this group's accumulator set has been used
         TileWalk w;
-        w.init(t0 + g, P.n_tiles, P.m_tiles);
-        const int count = (int)(t1 - t0);
-        for (int i = g; ok && i < count; i += SK_EPI_GROUPS, ++use, w.advance(SK_EPI_GROUPS, P.n_tiles, P.m_tiles)) {
+        w.init(blockIdx.x, gridDim.x, P.n_tiles, P.m_tiles, P.batch);
+        for (int i = 0; ok && w.valid(); ++i, w.advance()) {
+            if ((i & 1) != g) continue;                 // the other group's tile
             const int n_blk = w.n_blk, m_blk = w.m_blk, batch = w.batch;
+            const uint32_t use_now = use++;
             const int row = m_blk * BLOCK_M + row_in_tile;
             const bool row_ok = row < P.M;
             const int ea = row_ok ? __ldg(P.expo_a + (size_t)batch * P.M + row) : 0;
@@ -335,7 +309,7 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 eb_lo = min(eb_lo, __shfl_xor_sync(0xFFFFFFFFu, eb_lo, o));
                 eb_hi = max(eb_hi, __shfl_xor_sync(0xFFFFFFFFu, eb_hi, o));
             }
-            ok = mbar_wait_relaxed(tmem_full(g), use & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = mbar_wait_relaxed(tmem_full(g), use_now & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
