@@ -188,9 +188,12 @@ cudaError_t device_info(const DeviceInfo** out) {
                 d.err = e2;
                 return;
             }
-            if ((e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<1>::SMEM_BYTES)) != cudaSuccess ||
-                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<2>::SMEM_BYTES)) != cudaSuccess ||
-                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<3>::SMEM_BYTES)) != cudaSuccess) {
+            if ((e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<1>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<2>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<3>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<1>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<2>::SMEM_BYTES)) != cudaSuccess ||
+                (e2 = cudaFuncSetAttribute(gemm_i8_smallk_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmallKTraits<3>::SMEM_BYTES)) != cudaSuccess) {
                 d.err = e2;
                 return;
             }
@@ -281,6 +284,20 @@ cudaError_t encode_kmajor_f32_map(CUtensorMap* map, const float* src, int M, int
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(src), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// FP32 view of C as [batch][M][N] for the tensor stores of the short-K kernel: boxes of `cols` columns x 128 rows,
+// written from a shared-memory image with the swizzle that matches the box's row length (128 or 64 bytes).
+cudaError_t encode_c_store_map(CUtensorMap* map, float* C, int M, int N, int batch, long long batch_stride, int cols) {
+    if (!ensure_encode()) return cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)N * 4, (cuuint64_t)(batch > 1 ? batch_stride : (long long)M * N) * 4};
+    cuuint32_t box[3] = {(cuuint32_t)cols, (cuuint32_t)BLOCK_M, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          cols * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
@@ -531,9 +548,20 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
         Q.m_tiles = ceil_div(L.M, BLOCK_M); Q.n_tiles = ceil_div(L.N, SK_NT);
         Q.k_steps = ceil_div(L.K, UMMA_K);
         Q.e0 = e0;
+        // full-line output through shared memory and TMA stores where C's layout allows a tensor map
+        CUtensorMap map_cx = map_a, map_cy = map_a;
+        bool staged = (reinterpret_cast<uintptr_t>(a.C) & 15) == 0 && L.N % 4 == 0 && (L.batch == 1 || a.stride_c % 4 == 0) &&
+                   getenv("RGB200_SMALLK_DIRECT_STORES") == nullptr;
+        if (staged &&
+            (encode_c_store_map(&map_cx, a.C, L.M, L.N, L.batch, a.stride_c, SK_STAGE_X_COLS) != cudaSuccess ||
+             encode_c_store_map(&map_cy, a.C, L.M, L.N, L.batch, a.stride_c, SK_NT - SK_STAGE_X_COLS) != cudaSuccess)) {
+            staged = false;                     // a layout the encoder refuses: the threads store their rows themselves
+            map_cx = map_cy = map_a;
+        }
         const long long sk_tiles = (long long)L.batch * Q.m_tiles * Q.n_tiles;
         const int sk_grid = (int)(sk_tiles < dev.sm_count ? sk_tiles : dev.sm_count);
-        gemm_i8_smallk_kernel<S><<<sk_grid, SK_THREADS, SmallKTraits<S>::SMEM_BYTES, a.st>>>(map_a, map_b, Q);
+        if (staged) gemm_i8_smallk_kernel<S, true><<<sk_grid, SK_THREADS, SmallKTraits<S>::SMEM_BYTES, a.st>>>(map_a, map_b, map_cx, map_cy, Q);
+        else gemm_i8_smallk_kernel<S, false><<<sk_grid, SK_THREADS, SmallKTraits<S>::SMEM_BYTES, a.st>>>(map_a, map_b, map_cx, map_cy, Q);
         record(2);
         record(3);
         return cudaGetLastError();

@@ -17,6 +17,11 @@
 //     fastest, so the 128-row A tile (all S planes, the whole K) is loaded once per half row into one of two
 //     buffers; only the small B tiles stream through a ring of stages (see TileWalk).
 //   * k steps beyond K (zero padding of the 128-byte block) are not issued.
+//   * output: a thread owns one row of the tile (TMEM lane = row), so a warp-wide store of its results would touch
+//     32 different 128-byte lines per instruction, and the L1 store path, not HBM, bounded the kernel.  When C allows
+//     it (16-byte aligned base, rows and batches a multiple of four floats apart) the rounded tile goes into a
+//     swizzled shared-memory staging buffer instead (conflict-free 16-byte writes) and a dedicated thread sends it
+//     to C with TMA tensor stores, which also clip the ragged edges; otherwise the threads store their rows directly.
 // The arithmetic (level accumulators, exact INT64 sums, single rounding) is that of the general
 // kernel; see rgb200_mma.cuh.  Reference counterpart: gemm_wmma_i8<S> (repro_gemm_cuda/repro_gemm.cu:280-364);
 // the batched attention products it serves are listed as pending at gpt2_ops_suite/gpt2_ops_suite.cu:543-548.
@@ -26,16 +31,37 @@
 namespace rgb200 {
 
 constexpr int SK_NT = 48;                     // columns of C per tile
-constexpr int SK_B_STAGES = 5;
+constexpr int SK_B_STAGES = 4;
 constexpr int SK_EPI_GROUPS = 2;              // one per accumulator set
 constexpr int SK_GROUP_WARPS = 8;
 constexpr int SK_GROUP_THREADS = SK_GROUP_WARPS * 32;
-// warp 0: TMA producer; warp 1 and the last warp: the MMA issuers of accumulator set 0 and 1; between them the
-// sixteen epilogue warps
-constexpr int SK_THREADS = 64 + SK_EPI_GROUPS * SK_GROUP_THREADS + 32;    // 608
-constexpr int SK_SECOND_ISSUER_WARP = SK_THREADS / 32 - 1;
+// warp 0: TMA producer; warp 1 and warp 18: the MMA issuers of accumulator set 0 and 1; between them the sixteen
+// epilogue warps; warp 19: issues the TMA stores of the staged output tiles
+constexpr int SK_THREADS = 64 + SK_EPI_GROUPS * SK_GROUP_THREADS + 64;    // 640
+constexpr int SK_SECOND_ISSUER_WARP = SK_THREADS / 32 - 2;
+constexpr int SK_STORE_WARP = SK_THREADS / 32 - 1;
+// staged output tile: columns 0..31 as 128 rows of 128 bytes (128-byte swizzle), columns 32..47 as 128 rows of 64
+// bytes (64-byte swizzle); one TMA tensor store each
+constexpr int SK_STAGE_X_COLS = 32;
+constexpr int SK_STAGE_X_BYTES = BLOCK_M * SK_STAGE_X_COLS * 4;
+constexpr int SK_STAGE_Y_BYTES = BLOCK_M * (SK_NT - SK_STAGE_X_COLS) * 4;
+constexpr int SK_STAGE_BYTES = SK_STAGE_X_BYTES + SK_STAGE_Y_BYTES;
+enum : int { STATUS_WAIT_STAGE = 6 };         // a role gave up waiting for the output staging buffer
 
 // 32 lanes x 8 consecutive 32-bit columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 :: "l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    // no memory clobber: the staging buffer is read by the copy engine only, after the proxy fence (a volatile asm,
+    // so it stays behind these stores), and ordinary loads may be scheduled across the store
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d));
+}
+
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
@@ -130,8 +156,9 @@ struct SmallKTraits {
     static constexpr int TMEM_COLS = 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128 : 2 * ACC_COLS <= 256 ? 256 : 512;
     static constexpr int CPT = SK_NT / 2;                    // columns per epilogue thread
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = 2 * A_BYTES + SK_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
-                                      SK_EPI_GROUPS * SK_GROUP_WARPS * CPT * 4;
+    static constexpr int SMEM_BYTES = 2 * A_BYTES + SK_EPI_GROUPS * SK_STAGE_BYTES + SK_B_STAGES * B_STAGE_BYTES + 1024 +
+                                      BAR_BYTES + SK_EPI_GROUPS * SK_GROUP_WARPS * CPT * 4;
+    static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA");
     static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit TMEM");
     static_assert(CPT % 8 == 0, "the epilogue reads eight TMEM columns at a time");
 };
@@ -148,16 +175,25 @@ struct SmallKParams {
     int e0;
 };
 
-template <int S>
+// The exact rounding of four sums, kept out of line: the hot loops use it only for rows whose results may be
+// subnormal or overflow.
+__device__ __noinline__ uint4 round4_exact(long long t0, long long t1, long long t2, long long t3, int e0, int e1, int e2, int e3) {
+    return make_uint4(round_to_f32_bits(t0, e0), round_to_f32_bits(t1, e1), round_to_f32_bits(t2, e2), round_to_f32_bits(t3, e3));
+}
+
+// STAGED: C takes TMA tensor stores (tmap_cx / tmap_cy are valid); otherwise the threads store their rows.
+template <int S, bool STAGED>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_cx, const __grid_constant__ CUtensorMap tmap_cy,
                       const SmallKParams P) {
     using Tr = SmallKTraits<S>;
     constexpr int NT = SK_NT, CPT = Tr::CPT;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base = smem_base;
-    const uint32_t b_base = smem_base + 2 * Tr::A_BYTES;
+    const uint32_t c_base = smem_base + 2 * Tr::A_BYTES;
+    const uint32_t b_base = c_base + SK_EPI_GROUPS * SK_STAGE_BYTES;
     const uint32_t bar_base = b_base + SK_B_STAGES * Tr::B_STAGE_BYTES;
     auto a_full = [&](int i) { return bar_base + 8u * i; };
     auto a_empty = [&](int i) { return bar_base + 8u * (2 + i); };
@@ -166,8 +202,11 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     auto tmem_full = [&](int g) { return bar_base + 8u * (4 + 2 * SK_B_STAGES + g); };
     auto tmem_empty = [&](int g) { return bar_base + 8u * (6 + 2 * SK_B_STAGES + g); };
     const uint32_t tmem_slot = bar_base + 8u * (8 + 2 * SK_B_STAGES);
+    auto stage_free = [&](int g) { return bar_base + 8u * (10 + 2 * SK_B_STAGES + g); };
+    auto stage_full = [&](int g) { return bar_base + 8u * (12 + 2 * SK_B_STAGES + g); };
+    static_assert(8 * (14 + 2 * SK_B_STAGES) <= Tr::BAR_BYTES, "barrier area");
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint8_t* gen_bar = gen_base + 2 * Tr::A_BYTES + SK_B_STAGES * Tr::B_STAGE_BYTES;
+    uint8_t* gen_bar = gen_base + 2 * Tr::A_BYTES + SK_EPI_GROUPS * SK_STAGE_BYTES + SK_B_STAGES * Tr::B_STAGE_BYTES;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_bar + 8 * (8 + 2 * SK_B_STAGES));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_bar + 8 * (9 + 2 * SK_B_STAGES));
     int* eb_slots = reinterpret_cast<int*>(gen_bar + Tr::BAR_BYTES);
@@ -178,6 +217,7 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         for (int i = 0; i < 2; ++i) { mbar_init(a_full(i), 1); mbar_init(a_empty(i), SK_EPI_GROUPS); }
         for (int s = 0; s < SK_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
         for (int g = 0; g < SK_EPI_GROUPS; ++g) { mbar_init(tmem_full(g), 1); mbar_init(tmem_empty(g), SK_GROUP_THREADS); }
+        for (int g = 0; g < SK_EPI_GROUPS; ++g) { mbar_init(stage_free(g), 1); mbar_init(stage_full(g), SK_GROUP_THREADS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -270,6 +310,27 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 if (new_row) umma_commit(a_empty(cur_ab));
             }
         }
+    } else if (warp == SK_STORE_WARP) {
+        // ---------------------------------------------------------------- TMA stores of the staged tiles
+        // One thread follows the tile order: when all threads of the tile's group have written their rows it sends
+        // the two parts of the staging buffer to C and, once the copy engine has read them, hands the buffer back.
+        if (lane == 0 && STAGED) {
+            bool ok = true;
+            TileWalk w;
+            w.init(blockIdx.x, gridDim.x, P.n_tiles, P.m_tiles, P.batch);
+            for (uint32_t i = 0; w.valid(); ++i, w.advance()) {
+                const int g = i & 1;
+                if (!(ok = mbar_wait_relaxed(stage_full(g), (i >> 1) & 1u, abort_flag, P.status, STATUS_WAIT_STAGE))) break;
+                const uint32_t src = c_base + g * SK_STAGE_BYTES;
+                const int col = w.n_blk * NT;
+                tma_store_3d(&tmap_cx, src, col, w.m_blk * BLOCK_M, w.batch);
+                if (col + SK_STAGE_X_COLS < P.N) tma_store_3d(&tmap_cy, src + SK_STAGE_X_BYTES, col + SK_STAGE_X_COLS, w.m_blk * BLOCK_M, w.batch);
+                bulk_commit();
+                bulk_wait_read_all();
+                mbar_arrive(stage_free(g));
+            }
+            bulk_wait_all();
+        }
     } else {
         // ---------------------------------------------------------------- epilogue (two groups of eight warps)
         using TAcc = typename std::conditional<S == 1, int, long long>::type;
@@ -279,6 +340,18 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int half = (ew % SK_GROUP_WARPS) >> 2;   // which half of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
         int* eb_s = eb_slots + ew * CPT;
+        // where this thread's six 16-byte pieces go in the staging buffer: piece c of a row of the 32-column part at
+        // chunk c ^ (row % 8) of the row's 128 bytes, of the 16-column part at chunk c ^ ((row / 2) % 4) of its 64
+        // bytes - the images TMA's 128-byte and 64-byte swizzles expect, and free of bank conflicts for a warp's rows
+        uint32_t stage_off[CPT / 4];
+#pragma unroll
+        for (int j = 0; j < CPT / 4; ++j) {
+            const int c = half * (CPT / 4) + j;
+            stage_off[j] = c_base + g * SK_STAGE_BYTES +
+                           (c < SK_STAGE_X_COLS / 4
+                                ? row_in_tile * 128 + ((c ^ (row_in_tile & 7)) << 4)
+                                : SK_STAGE_X_BYTES + row_in_tile * 64 + (((c - SK_STAGE_X_COLS / 4) ^ ((row_in_tile >> 1) & 3)) << 4));
+        }
         bool ok = true;
         uint32_t use = 0;                              // how often this group's accumulator set has been used
         TileWalk w;
@@ -289,26 +362,11 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const uint32_t use_now = use++;
             const int row = m_blk * BLOCK_M + row_in_tile;
             const bool row_ok = row < P.M;
-            const int ea = row_ok ? __ldg(P.expo_a + (size_t)batch * P.M + row) : 0;
             const int col0 = n_blk * NT + half * CPT;
-            // The slot holds the column exponents already shifted into the exponent field of a float, and the warp
-            // learns their range: when every exponent this row can meet keeps any non-zero sum a normal number
-            // (the float of a non-zero sum has a biased exponent of 127..190, so E in [-126, 64] is safe), the
-            // rounding below needs no range check per output.
-            __syncwarp();
-            int eb_lo = 0x7FFFFFFF, eb_hi = -0x7FFFFFFF;
-            if (lane < CPT && col0 + lane < P.N) {
-                const int eb = __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane);
-                eb_s[lane] = eb << 23;
-                eb_lo = eb_hi = eb;
-            } else if (lane < CPT) {
-                eb_s[lane] = 0;
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                eb_lo = min(eb_lo, __shfl_xor_sync(0xFFFFFFFFu, eb_lo, o));
-                eb_hi = max(eb_hi, __shfl_xor_sync(0xFFFFFFFFu, eb_hi, o));
-            }
+            // the exponents are requested now and first used after the accumulators have been drained
+            const int ea = row_ok ? __ldg(P.expo_a + (size_t)batch * P.M + row) : 0;
+            const bool col_ok = lane < CPT && col0 + lane < P.N;
+            const int eb = col_ok ? __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane) : 0;
             ok = mbar_wait_relaxed(tmem_full(g), use_now & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
@@ -327,50 +385,74 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             }
             tc_fence_before();
             mbar_arrive(tmem_empty(g));
-            if (!row_ok || col0 >= P.N) continue;
-            // one rounding per output
-            uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
+            // (no lane leaves the iteration early: the warp-wide steps below need all of them)
+            // The slot holds the column exponents already shifted into the exponent field of a float, and the warp
+            // learns their range: when every exponent this row can meet keeps any non-zero sum a normal number
+            // (the float of a non-zero sum has a biased exponent of 127..190, so E in [-126, 64] is safe), the
+            // rounding below needs no range check per output.
+            __syncwarp();                               // the previous tile's reads of the slot are over
+            if (lane < CPT) eb_s[lane] = eb << 23;
+            int eb_lo = __reduce_min_sync(0xFFFFFFFFu, col_ok ? eb : 0x7FFFFFFF);
+            int eb_hi = __reduce_max_sync(0xFFFFFFFFu, col_ok ? eb : -0x7FFFFFFF);
+            if (eb_lo > eb_hi) eb_lo = eb_hi = 0;       // no column of this half lies inside the matrix
+            __syncwarp();
             const int ebase = ea + P.e0;
             const bool safe = ebase + eb_lo >= -126 && ebase + eb_hi <= 64;
             const uint32_t ebase23 = (uint32_t)ebase << 23;
+            const int4* eb4 = reinterpret_cast<const int4*>(eb_s);
+            // one rounding per output: one hardware conversion (round to nearest even, sign included), then the
+            // exponent is added in place; a zero sum converts to +0 and stays +0.  Rows that may meet subnormal or
+            // overflowing results take the exact routine instead (out of line: it is rare and large).
             auto round4 = [&](int j, uint32_t (&r)[4]) {
+                const int4 e4 = eb4[j >> 2];
+                const int e[4] = {e4.x, e4.y, e4.z, e4.w};
                 if (safe) {
-                    // one hardware conversion (round to nearest even, sign included), then the exponent is added in
-                    // place; a zero sum converts to +0 and stays +0
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint32_t fb = f32_bits(__ll2float_rn((long long)T[j + q]));
-                        r[q] = fb ? fb + ebase23 + (uint32_t)eb_s[j + q] : 0u;
+                        r[q] = fb ? fb + ebase23 + (uint32_t)e[q] : 0u;
                     }
-                } else {                                // subnormal or overflowing results are possible: exact path
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) r[q] = round_to_f32_bits(T[j + q], ebase + (eb_s[j + q] >> 23));
+                } else {
+                    const uint4 x = round4_exact(T[j], T[j + 1], T[j + 2], T[j + 3], ebase + (e[0] >> 23), ebase + (e[1] >> 23),
+                                                 ebase + (e[2] >> 23), ebase + (e[3] >> 23));
+                    r[0] = x.x; r[1] = x.y; r[2] = x.z; r[3] = x.w;
                 }
             };
-            const bool whole = col0 + CPT <= P.N;
-            if (whole && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
-#pragma unroll
-                for (int j = 0; j < CPT; j += 8) {
-                    uint32_t r[4], q[4];
-                    round4(j, r);
-                    round4(j + 4, q);
-                    st_global_256(dst + j, r[0], r[1], r[2], r[3], q[0], q[1], q[2], q[3]);
-                }
-            } else if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            if constexpr (STAGED) {
+                // rows and columns beyond the matrix hold zero sums (their operand rows were filled with zeros) and
+                // are clipped by the tensor store; every thread of the group takes part in the hand-over
+                ok = mbar_wait_relaxed(stage_free(g), (use_now & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_STAGE);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
 #pragma unroll
                 for (int j = 0; j < CPT; j += 4) {
                     uint32_t r[4];
                     round4(j, r);
-                    *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
+                    st_shared_128(stage_off[j / 4], r[0], r[1], r[2], r[3]);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(stage_full(g));
             } else {
+                uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
+                const bool whole = col0 + CPT <= P.N;
+                if (!row_ok || col0 >= P.N) {
+                    // nothing of this thread's part lies inside the matrix
+                } else if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                for (int j = 0; j < CPT; j += 4) {
-                    uint32_t r[4];
-                    round4(j, r);
+                    for (int j = 0; j < CPT; j += 4) {
+                        uint32_t r[4];
+                        round4(j, r);
+                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
+                    }
+                } else {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        if (col0 + j + q < P.N) dst[j + q] = r[q];
+                    for (int j = 0; j < CPT; j += 4) {
+                        uint32_t r[4];
+                        round4(j, r);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col0 + j + q < P.N) dst[j + q] = r[q];
+                    }
                 }
             }
         }
