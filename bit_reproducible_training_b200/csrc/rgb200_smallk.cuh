@@ -353,107 +353,126 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                 : SK_STAGE_X_BYTES + row_in_tile * 64 + (((c - SK_STAGE_X_COLS / 4) ^ ((row_in_tile >> 1) & 3)) << 4));
         }
         bool ok = true;
-        uint32_t use = 0;                              // how often this group's accumulator set has been used
         TileWalk w;
         w.init(blockIdx.x, gridDim.x, P.n_tiles, P.m_tiles, P.batch);
-        for (int i = 0; ok && w.valid(); ++i, w.advance()) {
-            if ((i & 1) != g) continue;                 // the other group's tile
+        if (g == 1 && w.valid()) w.advance();          // this group's first tile
+        // The exponents of a tile are requested one tile of this group ahead of their use.
+        int ea_next = 0, eb_next = 0;
+        bool col_ok_next = false;
+        auto request_exponents = [&]() {
+            const int row = w.m_blk * BLOCK_M + row_in_tile;
+            const int col = w.n_blk * NT + half * CPT + lane;
+            ea_next = row < P.M ? __ldg(P.expo_a + (size_t)w.batch * P.M + row) : 0;
+            col_ok_next = lane < CPT && col < P.N;
+            eb_next = col_ok_next ? __ldg(P.expo_b + (size_t)w.batch * P.N + col) : 0;
+        };
+        if (w.valid()) request_exponents();
+        for (uint32_t use = 0; ok && w.valid(); ++use) {   // use: how often this group's accumulator set has been used
             const int n_blk = w.n_blk, m_blk = w.m_blk, batch = w.batch;
-            const uint32_t use_now = use++;
+            const int ea = ea_next, eb = eb_next;
+            const bool col_ok = col_ok_next;
+            w.advance();                                // the other group's tile
+            if (w.valid()) w.advance();
+            if (w.valid()) request_exponents();
             const int row = m_blk * BLOCK_M + row_in_tile;
             const bool row_ok = row < P.M;
             const int col0 = n_blk * NT + half * CPT;
-            // the exponents are requested now and first used after the accumulators have been drained
-            const int ea = row_ok ? __ldg(P.expo_a + (size_t)batch * P.M + row) : 0;
-            const bool col_ok = lane < CPT && col0 + lane < P.N;
-            const int eb = col_ok ? __ldg(P.expo_b + (size_t)batch * P.N + col0 + lane) : 0;
-            ok = mbar_wait_relaxed(tmem_full(g), use_now & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            // accumulators -> exact sums in registers, then hand the set back to the MMA warp
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + g * Tr::ACC_COLS + half * CPT;
-            TAcc T[CPT];
-#pragma unroll
-            for (int c0 = 0; c0 < CPT; c0 += 8) {       // eight columns at a time keeps the register count low
-                int lv[Tr::LEVELS][8];
-#pragma unroll
-                for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 8; ++j) T[c0 + j] = combine_levels_short_k<S>(lv, j);
-            }
-            tc_fence_before();
-            mbar_arrive(tmem_empty(g));
-            // (no lane leaves the iteration early: the warp-wide steps below need all of them)
             // The slot holds the column exponents already shifted into the exponent field of a float, and the warp
-            // learns their range: when every exponent this row can meet keeps any non-zero sum a normal number
-            // (the float of a non-zero sum has a biased exponent of 127..190, so E in [-126, 64] is safe), the
-            // rounding below needs no range check per output.
+            // learns their range: when every exponent its rows can meet keeps any non-zero sum a normal number
+            // (the float of a non-zero sum has a biased exponent of 127..190, so E in [-126, 64] is safe), a sum is
+            // converted as soon as it is drained and only the exponent is added afterwards.
             __syncwarp();                               // the previous tile's reads of the slot are over
             if (lane < CPT) eb_s[lane] = eb << 23;
             int eb_lo = __reduce_min_sync(0xFFFFFFFFu, col_ok ? eb : 0x7FFFFFFF);
             int eb_hi = __reduce_max_sync(0xFFFFFFFFu, col_ok ? eb : -0x7FFFFFFF);
             if (eb_lo > eb_hi) eb_lo = eb_hi = 0;       // no column of this half lies inside the matrix
-            __syncwarp();
             const int ebase = ea + P.e0;
-            const bool safe = ebase + eb_lo >= -126 && ebase + eb_hi <= 64;
+            const bool fast = __all_sync(0xFFFFFFFFu, ebase + eb_lo >= -126 && ebase + eb_hi <= 64);
+            __syncwarp();
             const uint32_t ebase23 = (uint32_t)ebase << 23;
             const int4* eb4 = reinterpret_cast<const int4*>(eb_s);
-            // one rounding per output: one hardware conversion (round to nearest even, sign included), then the
-            // exponent is added in place; a zero sum converts to +0 and stays +0.  Rows that may meet subnormal or
-            // overflowing results take the exact routine instead (out of line: it is rare and large).
-            auto round4 = [&](int j, uint32_t (&r)[4]) {
-                const int4 e4 = eb4[j >> 2];
-                const int e[4] = {e4.x, e4.y, e4.z, e4.w};
-                if (safe) {
+            ok = mbar_wait_relaxed(tmem_full(g), use & 1u, abort_flag, P.status, STATUS_WAIT_TMEM_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + g * Tr::ACC_COLS + half * CPT;
+            // where four results go: the staging buffer, or (no tensor map for C) the thread's row of C
+            uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
+            const bool inside = row_ok && col0 < P.N;
+            const bool vec = inside && col0 + CPT <= P.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+            auto emit = [&](int j, const uint32_t (&r)[4]) {
+                if constexpr (STAGED) {
+                    st_shared_128(stage_off[j / 4], r[0], r[1], r[2], r[3]);
+                } else if (vec) {
+                    *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
+                } else if (inside) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint32_t fb = f32_bits(__ll2float_rn((long long)T[j + q]));
-                        r[q] = fb ? fb + ebase23 + (uint32_t)e[q] : 0u;
-                    }
-                } else {
-                    const uint4 x = round4_exact(T[j], T[j + 1], T[j + 2], T[j + 3], ebase + (e[0] >> 23), ebase + (e[1] >> 23),
-                                                 ebase + (e[2] >> 23), ebase + (e[3] >> 23));
-                    r[0] = x.x; r[1] = x.y; r[2] = x.z; r[3] = x.w;
+                    for (int q = 0; q < 4; ++q)
+                        if (col0 + j + q < P.N) dst[j + q] = r[q];
                 }
             };
-            if constexpr (STAGED) {
-                // rows and columns beyond the matrix hold zero sums (their operand rows were filled with zeros) and
-                // are clipped by the tensor store; every thread of the group takes part in the hand-over
-                ok = mbar_wait_relaxed(stage_free(g), (use_now & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_STAGE);
-                ok = __all_sync(0xFFFFFFFFu, ok);
+            // rows and columns beyond the matrix hold zero sums (their operand rows were filled with zeros) and are
+            // clipped by the tensor store; every thread of the group takes part in the hand-over of the staging buffer
+            auto wait_stage = [&]() {
+                if constexpr (STAGED) {
+                    ok = mbar_wait_relaxed(stage_free(g), (use & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_STAGE);
+                    ok = __all_sync(0xFFFFFFFFu, ok);
+                }
+            };
+            if (fast) {
+                // accumulators -> exact sums -> one hardware conversion each (round to nearest even, sign included),
+                // eight columns at a time, then the set goes back to its MMA issuer
+                uint32_t fb[CPT];
+#pragma unroll
+                for (int c0 = 0; c0 < CPT; c0 += 8) {
+                    int lv[Tr::LEVELS][8];
+#pragma unroll
+                    for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) fb[c0 + j] = f32_bits(__ll2float_rn((long long)combine_levels_short_k<S>(lv, j)));
+                }
+                tc_fence_before();
+                mbar_arrive(tmem_empty(g));
+                wait_stage();
                 if (!ok) break;
+                // the exponent is added in place; a zero sum converted to +0 and stays +0
 #pragma unroll
                 for (int j = 0; j < CPT; j += 4) {
-                    uint32_t r[4];
-                    round4(j, r);
-                    st_shared_128(stage_off[j / 4], r[0], r[1], r[2], r[3]);
+                    const int4 e4 = eb4[j >> 2];
+                    const uint32_t r[4] = {fb[j] ? fb[j] + ebase23 + (uint32_t)e4.x : 0u, fb[j + 1] ? fb[j + 1] + ebase23 + (uint32_t)e4.y : 0u,
+                                           fb[j + 2] ? fb[j + 2] + ebase23 + (uint32_t)e4.z : 0u, fb[j + 3] ? fb[j + 3] + ebase23 + (uint32_t)e4.w : 0u};
+                    emit(j, r);
                 }
+            } else {
+                // some result of this warp's rows may be subnormal or overflow: exact sums are kept and rounded by the
+                // exact routine (out of line: it is rare and large)
+                TAcc T[CPT];
+#pragma unroll
+                for (int c0 = 0; c0 < CPT; c0 += 8) {
+                    int lv[Tr::LEVELS][8];
+#pragma unroll
+                    for (int L = 0; L < Tr::LEVELS; ++L) tmem_ld8(t_row + L * NT + c0, lv[L]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) T[c0 + j] = combine_levels_short_k<S>(lv, j);
+                }
+                tc_fence_before();
+                mbar_arrive(tmem_empty(g));
+                wait_stage();
+                if (!ok) break;
+#pragma unroll 1
+                for (int j = 0; j < CPT; j += 4) {
+                    const int4 e4 = eb4[j >> 2];
+                    const uint4 x = round4_exact(T[j], T[j + 1], T[j + 2], T[j + 3], ebase + (e4.x >> 23), ebase + (e4.y >> 23),
+                                                 ebase + (e4.z >> 23), ebase + (e4.w >> 23));
+                    const uint32_t r[4] = {x.x, x.y, x.z, x.w};
+                    emit(j, r);
+                }
+            }
+            if constexpr (STAGED) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(stage_full(g));
-            } else {
-                uint32_t* dst = reinterpret_cast<uint32_t*>(P.C + (size_t)batch * P.stride_c + (size_t)row * P.N + col0);
-                const bool whole = col0 + CPT <= P.N;
-                if (!row_ok || col0 >= P.N) {
-                    // nothing of this thread's part lies inside the matrix
-                } else if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-                    for (int j = 0; j < CPT; j += 4) {
-                        uint32_t r[4];
-                        round4(j, r);
-                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[0], r[1], r[2], r[3]);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < CPT; j += 4) {
-                        uint32_t r[4];
-                        round4(j, r);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            if (col0 + j + q < P.N) dst[j + q] = r[q];
-                    }
-                }
             }
         }
     }
