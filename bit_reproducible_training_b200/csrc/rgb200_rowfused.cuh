@@ -15,9 +15,11 @@
 //           would have produced - one k block (two chunks) per MMA stage;
 //   MMA     one thread issues the same level-accumulating MMAs as the general kernel;
 //   finish  the sixteen warps drain TMEM, rebuild the exact sums, round once and store C.
-// Shared memory holds only two 32 KiB FP32 chunks, too few bytes in flight to keep HBM busy; the producer
-// therefore also issues TMA prefetches into L2 eight chunks ahead of its loads, across pass and tile
-// boundaries, and the loads themselves find their data in L2.
+// Shared memory holds only two 32 KiB FP32 landing stages beside the MMA stages, too few bytes in flight to keep
+// HBM busy; so (a) the producer also issues TMA prefetches into L2 a few chunks ahead of its loads, across pass
+// and tile boundaries, and the loads themselves find their data in L2, and (b) during pass 1, when the int8 stages
+// of A hold nothing (the previous block's MMAs are over, this block's digits do not exist yet), their memory
+// serves as S more landing stages: pass 1 keeps 2 + S chunks in flight.
 // The arithmetic is that of the general kernel (rgb200_mma.cuh) and of the split pre-pass
 // (rgb200_prepass.cuh); only where the digits of A live differs.  Reference counterparts:
 // quantize_kmajor + gemm_wmma_i8 (repro_gemm_cuda/repro_gemm.cu:54-79, 280-364).
@@ -37,7 +39,7 @@ constexpr int RF_CHUNKS_PER_BLOCK = BLOCK_K / RF_CHUNK_K;
 constexpr int RF_LANES_PER_ROW = RF_CHUNK_K / 4;          // one 16-byte load per lane
 constexpr int RF_ROWS_PER_LOAD = 32 / RF_LANES_PER_ROW;   // rows a warp-wide load covers
 constexpr int RF_ROW_ITERS = 8 / RF_ROWS_PER_LOAD;        // loads per warp and chunk (a warp owns eight rows)
-constexpr int RF_PREFETCH = 8;                // chunks requested into L2 ahead of the loads (8 x 32 KiB per SM)
+constexpr int RF_PREFETCH = 4;                // chunks requested into L2 ahead of the loads (more than a few evict the block that pass 2 re-reads)
 constexpr int RF_F_STAGE_BYTES = BLOCK_M * RF_CHUNK_K * 4;
 constexpr int RF_WORK_WARPS = 16;             // converter + epilogue warps
 constexpr int RF_WORK_THREADS = RF_WORK_WARPS * 32;
@@ -53,6 +55,9 @@ struct RowFusedTraits {
     static constexpr int ACC_COLS = LEVELS * RF_NT;
     static constexpr int TMEM_COLS = ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     static constexpr int CPT = RF_NT / 4;     // sixteen columns per epilogue thread
+    // FP32 landing stages that pass 1 borrows from the int8 stages of A, and the length of its chunk cycle
+    static constexpr int X_STAGES = RF_A_STAGES * A_STAGE_BYTES / RF_F_STAGE_BYTES;
+    static constexpr int P1_CYCLE = RF_F_STAGES + X_STAGES;
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM_BYTES = RF_F_STAGES * RF_F_STAGE_BYTES + RF_A_STAGES * A_STAGE_BYTES + RF_B_STAGES * B_STAGE_BYTES + 1024 + BAR_BYTES +
                                       RF_WORK_WARPS * CPT * 4 /* column exponents */ + BLOCK_M * 4 /* row exponents */;
@@ -95,6 +100,9 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const uint32_t rows_bar = bar_base + 8u * (NBAR + 2);       // every warp has published its rows' exponents
     const uint32_t done_bar = bar_base + 8u * (NBAR + 3);       // every warp has finished the tile's epilogue
     const uint32_t tmem_slot = bar_base + 8u * (NBAR + 4);
+    auto x_full = [&](int s) { return bar_base + 8u * (NBAR + 6 + s); };
+    auto x_empty = [&](int s) { return bar_base + 8u * (NBAR + 6 + Tr::X_STAGES + s); };
+    static_assert(8 * (NBAR + 6 + 2 * Tr::X_STAGES) <= Tr::BAR_BYTES, "barrier area");
     uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
     uint8_t* gen_a = gen_base;
     const uint8_t* gen_f = gen_base + RF_A_STAGES * Tr::A_STAGE_BYTES + RF_B_STAGES * Tr::B_STAGE_BYTES;
@@ -111,6 +119,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int s = 0; s < RF_A_STAGES; ++s) { mbar_init(a_full(s), RF_WORK_WARPS); mbar_init(a_empty(s), 1); }
         for (int s = 0; s < RF_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
         for (int s = 0; s < RF_F_STAGES; ++s) { mbar_init(f_full(s), 1); mbar_init(f_empty(s), RF_WORK_WARPS); }
+        for (int s = 0; s < Tr::X_STAGES; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), RF_WORK_WARPS); }
         mbar_init(tmem_full_bar, 1);
         mbar_init(tmem_empty_bar, RF_WORK_THREADS);
         mbar_init(rows_bar, RF_WORK_WARPS);
@@ -128,8 +137,17 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (FP32 chunks of A, planes of B)
         if (lane == 0) {
-            uint32_t f_it = 0, b_it = 0;
+            uint32_t f_it = 0, b_it = 0, x_it = 0;
             bool ok = true;
+            // pass 1 only: a chunk into one of the stages borrowed from A's int8 stages
+            auto load_chunk_x = [&](int c, int m_blk, int batch) {
+                const int s = x_it % Tr::X_STAGES;
+                if (!mbar_wait(x_empty(s), ((x_it / Tr::X_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY)) return false;
+                mbar_arrive_expect_tx(x_full(s), RF_F_STAGE_BYTES);
+                tma_load_3d(a_base + s * RF_F_STAGE_BYTES, &tmap_a, x_full(s), c * RF_CHUNK_K, m_blk * BLOCK_M, batch);
+                ++x_it;
+                return true;
+            };
             auto load_chunk = [&](int c, int m_blk, int batch) {
                 const int s = f_it % RF_F_STAGES;
                 if (!mbar_wait(f_empty(s), ((f_it / RF_F_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY)) return false;
@@ -138,8 +156,10 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 ++f_it;
                 return true;
             };
-            // Chunk order (the work warps consume in the same order): per tile all chunks for pass 1, then all chunks
-            // again for pass 2, with B's planes of a k block in front of that block's chunks.  A second cursor
+            // Chunk order (the work warps consume in the same order): per tile all chunks for pass 1 - chunk c into a
+            // landing stage when c modulo (2 + S) is below two, else into a borrowed stage - then all chunks again
+            // for pass 2, landing stages only, with B's planes of a k block in front of that block's chunks.  The
+            // borrowed stages are free once the previous tile's MMAs are over (its tmem_full commit).  A second cursor
             // runs RF_PREFETCH chunks ahead of the loads and only asks for the chunk to be brought into L2, so that
             // enough bytes are on their way from HBM although just RF_F_STAGES chunks fit shared memory.
             struct Cursor { int tile, pass, c, batch, m_blk; };
@@ -153,6 +173,8 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
                              ::"l"(&tmap_a), "r"(x.c * RF_CHUNK_K), "r"(x.m_blk * BLOCK_M), "r"(x.batch) : "memory");
             };
+            uint32_t tile_it = 0;                 // tiles whose first pass has been started
+            bool x_open = true;                   // the borrowed stages may be written for the current tile's first pass
             Cursor cur{(int)blockIdx.x, 0, 0, 0, 0}, ahead{(int)blockIdx.x, 0, 0, 0, 0};
             place(cur);
             place(ahead);
@@ -165,10 +187,21 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), (cur.c / RF_CHUNKS_PER_BLOCK) * BLOCK_K, 0, 0, cur.batch);
                     ++b_it;
                 }
-                if (!(ok = load_chunk(cur.c, cur.m_blk, cur.batch))) break;
+                if (cur.pass == 0 && cur.c % Tr::P1_CYCLE >= RF_F_STAGES) {
+                    if (!x_open) {
+                        // the previous tile's MMAs still read the int8 stages until its last commit has arrived
+                        if (!(ok = mbar_wait(tmem_full_bar, (tile_it - 1) & 1u, abort_flag, P.status, STATUS_WAIT_FULL))) break;
+                        x_open = true;
+                    }
+                    if (!(ok = load_chunk_x(cur.c, cur.m_blk, cur.batch))) break;
+                } else {
+                    if (!(ok = load_chunk(cur.c, cur.m_blk, cur.batch))) break;
+                }
                 prefetch(ahead);
                 step(ahead);
+                const int tile_before = cur.tile;
                 step(cur);
+                if (cur.tile != tile_before) { ++tile_it; x_open = false; }
             }
             if (!ok) {
                 // abort: let copies that are still in flight land before the CTA gives up its shared memory
@@ -184,6 +217,10 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (uint32_t j = 0; j < (f_it < (uint32_t)RF_F_STAGES ? f_it : (uint32_t)RF_F_STAGES); ++j) {
                     const uint32_t i2 = f_it - 1 - j;
                     drain(f_full(i2 % RF_F_STAGES), (i2 / RF_F_STAGES) & 1u);
+                }
+                for (uint32_t j = 0; j < (x_it < (uint32_t)Tr::X_STAGES ? x_it : (uint32_t)Tr::X_STAGES); ++j) {
+                    const uint32_t i2 = x_it - 1 - j;
+                    drain(x_full(i2 % Tr::X_STAGES), (i2 / Tr::X_STAGES) & 1u);
                 }
             }
         }
@@ -232,23 +269,26 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // swizzled digit stores of the lane groups fall into different bank groups.
         const int cl = lane % RF_LANES_PER_ROW;        // which four k of the chunk
         const int rsel = lane / RF_LANES_PER_ROW;
-        uint32_t f_it = 0, a_it = 0, tile_it = 0;
+        uint32_t f_it = 0, a_it = 0, tile_it = 0, x_it = 0;
         bool ok = true;
-        // one FP32 chunk into the running row maxima
-        auto max_chunk = [&](float (&m)[RF_ROW_ITERS]) {
-            const int s = f_it % RF_F_STAGES;
-            bool got = mbar_wait_relaxed(f_full(s), (f_it / RF_F_STAGES) & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+        // one FP32 chunk into the running row maxima; chunk c of the pass sits in a landing stage or in a borrowed one
+        auto max_chunk = [&](int c, float (&m)[RF_ROW_ITERS]) {
+            const bool borrowed = c % Tr::P1_CYCLE >= RF_F_STAGES;
+            const int s = borrowed ? x_it % Tr::X_STAGES : f_it % RF_F_STAGES;
+            const uint32_t full = borrowed ? x_full(s) : f_full(s), empty = borrowed ? x_empty(s) : f_empty(s);
+            const uint32_t parity = borrowed ? (x_it / Tr::X_STAGES) & 1u : (f_it / RF_F_STAGES) & 1u;
+            bool got = mbar_wait_relaxed(full, parity, abort_flag, P.status, STATUS_WAIT_FULL);
             got = __all_sync(0xFFFFFFFFu, got);
             if (!got) return false;
-            const uint8_t* chunk = gen_f + s * RF_F_STAGE_BYTES;
+            const uint8_t* chunk = borrowed ? gen_a + s * RF_F_STAGE_BYTES : gen_f + s * RF_F_STAGE_BYTES;
 #pragma unroll
             for (int i = 0; i < RF_ROW_ITERS; ++i) {
                 const int r = cw * 8 + rsel * RF_ROW_ITERS + i;
                 m[i] = abs4max(m[i], *reinterpret_cast<const float4*>(chunk + r * (RF_CHUNK_K * 4) + cl * 16));
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(f_empty(s));
-            ++f_it;
+            if (lane == 0) mbar_arrive(empty);
+            if (borrowed) ++x_it; else ++f_it;
             return true;
         };
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_it) {
@@ -257,7 +297,7 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             float m[RF_ROW_ITERS];
 #pragma unroll
             for (int i = 0; i < RF_ROW_ITERS; ++i) m[i] = 0.0f;
-            for (int c = 0; ok && c < RF_CHUNKS_PER_BLOCK * P.k_blocks; ++c) ok = max_chunk(m);
+            for (int c = 0; ok && c < RF_CHUNKS_PER_BLOCK * P.k_blocks; ++c) ok = max_chunk(c, m);
             if (!ok) break;
             int e[RF_ROW_ITERS];
             float f1[RF_ROW_ITERS];
@@ -272,6 +312,13 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (cl == 0) ea_rows[cw * 8 + rsel * RF_ROW_ITERS + i] = e[i];    // the previous tile's epilogue has finished reading (done_bar)
             }
             all_plain = __all_sync(0xFFFFFFFFu, all_plain);
+            // every warp has left pass 1 - the borrowed stages are about to be overwritten with digits - and every
+            // warp's row exponents are in ea_rows before any warp's epilogue reads them
+            __syncwarp();
+            if (lane == 0) mbar_arrive(rows_bar);
+            ok = mbar_wait_relaxed(rows_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
             // pass 2: digits into the swizzled stages
             for (int kb = 0; kb < P.k_blocks; ++kb, ++a_it) {
                 const int sa_i = a_it % RF_A_STAGES;
@@ -309,12 +356,6 @@ gemm_i8_rowfused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 __syncwarp();
                 if (lane == 0) mbar_arrive(a_full(sa_i));
             }
-            if (!ok) break;
-            // every warp's row exponents are in ea_rows before any warp's epilogue reads them
-            __syncwarp();
-            if (lane == 0) mbar_arrive(rows_bar);
-            ok = mbar_wait_relaxed(rows_bar, tile_it & 1u, abort_flag, P.status, STATUS_WAIT_FULL);
-            ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             // epilogue: 32 rows x 16 columns per warp
             const int row_in_tile = quarter * 32 + lane;
