@@ -401,7 +401,7 @@ void launch_split(const float* src, bool k_major, const float* given_max, uint32
         if (given_max)
             maxima_to_bits_kernel<<<ceil_div(batch * R, 256), 256, 0, st>>>(given_max, maxbits, batch * R);
         else
-            colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), ceil_div(K, COLMAX_K_PER_CTA), batch), PREPASS_THREADS, 0, st>>>(
+            colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), (ceil_div(K, COLMAX_K_PER_CTA) < COLMAX_MAX_GRID_Y ? ceil_div(K, COLMAX_K_PER_CTA) : COLMAX_MAX_GRID_Y), batch), PREPASS_THREADS, 0, st>>>(
                 src, maxbits, R, K, batch_stride);
         // about eight CTAs per SM in total; each walks over the k tiles of its 32 rows
         const int r_blocks = ceil_div(R, 32), k_tiles = Kp / BLOCK_K;
@@ -1175,7 +1175,7 @@ int rgb200_absmax(const float* X, int R, int K, int k_strided, float* out, void*
     } else {
         // non-negative floats order like their bit patterns: accumulate the maxima in place as integers
         if ((e = cudaMemsetAsync(out, 0, (size_t)R * sizeof(float), st)) != cudaSuccess) return e;
-        colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), ceil_div(K, COLMAX_K_PER_CTA), 1), PREPASS_THREADS, 0, st>>>(
+        colmax_kstrided_kernel<<<dim3(ceil_div(R, 128), (ceil_div(K, COLMAX_K_PER_CTA) < COLMAX_MAX_GRID_Y ? ceil_div(K, COLMAX_K_PER_CTA) : COLMAX_MAX_GRID_Y), 1), PREPASS_THREADS, 0, st>>>(
             X, reinterpret_cast<uint32_t*>(out), R, K, 0);
     }
     return cudaGetLastError();

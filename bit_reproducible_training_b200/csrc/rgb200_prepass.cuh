@@ -260,9 +260,10 @@ split_kmajor_short_kernel(const KmajorOperand first, const KmajorOperand second,
 // k-strided operand: element (r, k) at src[k*R + r]   (B without trans_b, A with trans_a).
 // Pass 1: column maxima over K with an integer atomicMax (|x| >= 0 orders like its bit pattern,
 // so the result is exact and order-free).  maxbits[batch][R] must be zero on entry.
-// grid = (ceil(R / 128), ceil(K / 64), batch), block = 256 threads = 32 column groups x 8 k-rows.
+// grid = (ceil(R / 128), min(ceil(K / 64), 65535), batch), block = 256 threads = 32 column groups x 8 k-rows.
 // ---------------------------------------------------------------------------------------------
 constexpr int COLMAX_K_PER_CTA = 64;
+constexpr int COLMAX_MAX_GRID_Y = 65535;       // hardware limit on gridDim.y; longer K is walked by the CTAs
 
 __global__ void __launch_bounds__(PREPASS_THREADS)
 colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ maxbits, int R, int K,
@@ -272,10 +273,12 @@ colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ max
     const int b = blockIdx.z;
     const float* s = src + (size_t)b * src_batch_stride;
     const int r0 = blockIdx.x * 128 + tx * 4;
-    const int k_lo = blockIdx.y * COLMAX_K_PER_CTA;
-    const int k_hi = min(K, k_lo + COLMAX_K_PER_CTA);
     float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
     const bool vec = (R & 3) == 0 && ((reinterpret_cast<uintptr_t>(s) & 15) == 0);
+    // a CTA takes the k chunks blockIdx.y, blockIdx.y + gridDim.y, ... (the launch caps gridDim.y at the hardware limit)
+    for (long long k_lo_ll = (long long)blockIdx.y * COLMAX_K_PER_CTA; k_lo_ll < K; k_lo_ll += (long long)gridDim.y * COLMAX_K_PER_CTA) {
+    const int k_lo = (int)k_lo_ll;
+    const int k_hi = (int)min((long long)K, k_lo_ll + COLMAX_K_PER_CTA);
     if (vec) {
         if (r0 < R) {
             const float4* p = reinterpret_cast<const float4*>(s + (size_t)(k_lo + ty) * R + r0);
@@ -304,6 +307,7 @@ colmax_kstrided_kernel(const float* __restrict__ src, uint32_t* __restrict__ max
             if (r0 + 2 < R) m2 = fmaxf(m2, fabsf(__ldg(p + 2)));
             if (r0 + 3 < R) m3 = fmaxf(m3, fabsf(__ldg(p + 3)));
         }
+    }
     }
     red[ty][tx * 4 + 0] = m0; red[ty][tx * 4 + 1] = m1; red[ty][tx * 4 + 2] = m2; red[ty][tx * 4 + 3] = m3;
     __syncthreads();

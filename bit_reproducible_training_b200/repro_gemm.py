@@ -7,6 +7,7 @@ only for device memory and streams; all arithmetic happens in librgb200.so.  The
 the reference's binding sends CPU tensors to its CPU implementation, this one refuses them.
 """
 import ctypes as C
+import os
 import enum
 from dataclasses import dataclass
 
@@ -162,6 +163,28 @@ def _workspace(nbytes, device):
     return ws
 
 
+class ReproGemmIncomplete(RuntimeError):
+    """A kernel gave up a bounded wait and left its output incomplete; ``status`` holds the code of the wait."""
+
+    def __init__(self, status, where):
+        super().__init__("%s: a bounded wait inside the kernel expired (status %d); the result is incomplete" % (where, status))
+        self.status = status
+
+
+def check_status_enabled():
+    """Opt-in check of the workspace's status word after the allocating wrappers (gemm, gemm_batched): set
+    RGB200_CHECK_STATUS=1.  It synchronises the stream, so it is off by default."""
+    return os.environ.get("RGB200_CHECK_STATUS", "0") not in ("", "0")
+
+
+def _raise_if_incomplete(ws, where):
+    if check_status_enabled():
+        torch.cuda.current_stream(ws.device).synchronize()
+        st = workspace_status(ws)
+        if st != 0:
+            raise ReproGemmIncomplete(st, where)
+
+
 def _check(t, n, name):
     if t.dtype != torch.float32:
         raise TypeError("%s must be float32" % name)
@@ -187,6 +210,7 @@ def gemm(A, B, M, N, K, trans_a=False, trans_b=False, slices=3, split_k=1, algo=
         rc = repro_gemm_fp32_ws(A, B, out, M, N, K, cfg, ws)
     if rc != cudaSuccess:
         raise ReproGemmError(rc, "repro_gemm_fp32_ws")
+    _raise_if_incomplete(ws, "gemm")
     return out
 
 
@@ -204,6 +228,7 @@ def gemm_batched(A, B, batch, M, N, K, trans_a=False, trans_b=False, slices=3):
         rc = repro_gemm_fp32_batched_ws(A, B, out, M, N, K, batch, M * K, K * N, M * N, cfg, ws)
     if rc != cudaSuccess:
         raise ReproGemmError(rc, "repro_gemm_fp32_batched_ws")
+    _raise_if_incomplete(ws, "gemm_batched")
     return out
 
 

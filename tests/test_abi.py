@@ -313,3 +313,15 @@ def test_cxx_conv_caller_builds_against_the_shim_and_links_the_library(L, tmp_pa
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
     assert [int(v) for v in out[:5]] == [0, 0, 0, rg.cudaErrorInvalidValue, rg.cudaErrorInvalidValue]
     assert [int(v) for v in out[5:]] == [25, 28, 28, 78400, 100 * 6 * 28 * 28]
+
+
+def test_status_check_of_the_python_wrappers_is_opt_in(monkeypatch):
+    from bit_reproducible_training_b200 import repro_gemm as rg
+    monkeypatch.delenv("RGB200_CHECK_STATUS", raising=False)
+    assert not rg.check_status_enabled()
+    monkeypatch.setenv("RGB200_CHECK_STATUS", "0")
+    assert not rg.check_status_enabled()
+    monkeypatch.setenv("RGB200_CHECK_STATUS", "1")
+    assert rg.check_status_enabled()
+    err = rg.ReproGemmIncomplete(4, "gemm")
+    assert err.status == 4 and "incomplete" in str(err)

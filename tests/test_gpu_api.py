@@ -325,3 +325,19 @@ def test_scatter_epilogue_emulated_on_one_gpu():
             got = rg.round_scattered(bufs[o], world, max_a[o * rows:(o + 1) * rows], max_b, rows, N, S).cpu().numpy()
             assert np.array_equal(got.view(np.uint32), want[o * rows:(o + 1) * rows].view(np.uint32)), (world, S, o)
     assert rg.scatter_buffer_elems(300, 64, 2, 3) == 0          # rows per owner must be whole 128-row tiles
+
+
+def test_wrappers_check_the_status_word_when_asked(monkeypatch):
+    """RGB200_CHECK_STATUS=1: gemm and gemm_batched synchronise and read the workspace's status word; a run whose
+    waits all completed passes the check and returns the same bits."""
+    import numpy as np
+    g = fx.Rng(77)
+    M, N, K = 130, 70, 200
+    A, B = g.normal(M * K), g.normal(K * N)
+    monkeypatch.delenv("RGB200_CHECK_STATUS", raising=False)
+    plain = rg.gemm(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), M, N, K).cpu().numpy()
+    monkeypatch.setenv("RGB200_CHECK_STATUS", "1")
+    checked = rg.gemm(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), M, N, K).cpu().numpy()
+    assert np.array_equal(plain.view(np.uint32), checked.view(np.uint32))
+    out = rg.gemm_batched(torch.from_numpy(np.concatenate([A, A])).cuda(), torch.from_numpy(np.concatenate([B, B])).cuda(), 2, M, N, K)
+    assert np.array_equal(out[1].cpu().numpy().view(np.uint32), plain.view(np.uint32))

@@ -152,3 +152,13 @@ def test_batched_with_k_ranges_and_every_slice_count():
                 want = oracle.gemm(A[b * sa:b * sa + M * K], B[b * sb:b * sb + K * N], M, N, K, S=S)
                 assert np.array_equal(o[b * sc:b * sc + M * N].view(np.uint32), want.view(np.uint32).reshape(-1)), (S, split, b)
                 assert np.isnan(o[b * sc + M * N:(b + 1) * sc]).all()
+
+
+def test_k_strided_operands_longer_than_the_grid_limit():
+    """K above 65535 x 64: the column-maximum pass of a k-strided operand cannot give every 64-k chunk a CTA of
+    its own along grid.y and has to walk them; both operands are k-strided here (A transposed, B not)."""
+    M, N, K = 16, 16, 65535 * 64 + 777
+    g = fx.Rng(4242)
+    A, B = g.normal(M * K), g.normal(K * N)
+    At = np.ascontiguousarray(A.reshape(M, K).T).reshape(-1)
+    check(At, B, M, N, K, True, False, 1)

@@ -47,7 +47,8 @@ def check(got, want, what):
 
 @pytest.mark.parametrize("S", [1, 2, 3])
 @pytest.mark.parametrize("shape", [(133, 77, 64), (300, 200, 100), (129, 1000, 128), (64, 64, 7), (1, 1, 1),
-                                   (513, 33, 31), (128, 32, 32), (1024, 1024, 64), (257, 4100, 96)])
+                                   (513, 33, 31), (128, 32, 32), (1024, 1024, 64), (257, 4100, 96),
+                                   (40, 8, 64), (200, 20, 100), (130, 44, 64)])   # N below one store box, and a clipped second box
 def test_short_k_every_transposition(shape, S):
     M, N, K = shape
     g = fx.Rng(1000 + M + N + K)
