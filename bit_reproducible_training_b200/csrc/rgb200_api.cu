@@ -581,12 +581,14 @@ cudaError_t run(const Layout& L, const RunArgs& a, const DeviceInfo& dev) {
     P.m_tiles = ceil_div(L.M, BLOCK_M);
     P.n_tiles = ceil_div(L.N, tile_n);
     P.e0 = e0;
-    P.scatter_rows = 0; P.scatter_slot = 0;
+    P.scatter_rows = 0; P.scatter_slot = 0; P.scatter_rot = 0;
     P.c_image_rows = a.c_image_rows;
     for (int i = 0; i < 8; ++i) P.scatter[i] = nullptr;
     if (a.scatter) {
         P.scatter_rows = L.M / a.scatter_world;
         P.scatter_slot = a.scatter_rank;
+        // start with the rows of the next rank, end with this rank's own (see GemmParams::scatter_rot)
+        P.scatter_rot = ((a.scatter_rank + 1) % a.scatter_world) * (P.scatter_rows / BLOCK_M);
         for (int i = 0; i < a.scatter_world; ++i) P.scatter[i] = a.scatter[i];
         P.partial = a.scatter[a.scatter_rank];      // non-null marks the INT64 path; every row is redirected
         P.C = nullptr;

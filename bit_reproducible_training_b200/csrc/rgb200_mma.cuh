@@ -94,6 +94,10 @@ struct GemmParams {
     // scatter_rows == 0: off; otherwise a multiple of 128.
     long long* scatter[8];
     int scatter_rows, scatter_slot;
+    // Row tiles are visited starting at tile scatter_rot (and wrapping around): every rank starts with the rows of the
+    // owner after itself and ends with its own, so that at any moment the ranks send to different owners and no
+    // owner's NVLink ingress has to take all of them at once.
+    int scatter_rot;
     // Image-major C (kernels built with IMAGE_MAJOR_C): row r = image * c_image_rows + place, and element
     // (r, col) is stored at C[(image * N + col) * c_image_rows + place], the [N, F, OH, OW] / [N, C, H, W]
     // layouts of a convolution's results.  A warp's 32 rows are consecutive places, so each column is one
@@ -255,6 +259,10 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& P, long long t
     int rows_here = min(GROUP, P.m_tiles - g * GROUP);
     c.n_blk = in_g / rows_here;
     c.m_blk = g * GROUP + (in_g - c.n_blk * rows_here);
+    if (P.scatter_rot) {
+        c.m_blk += P.scatter_rot;
+        if (c.m_blk >= P.m_tiles) c.m_blk -= P.m_tiles;
+    }
     c.kb_begin = (int)((long long)P.k_blocks * c.z / P.split);
     c.kb_end = (int)((long long)P.k_blocks * (c.z + 1) / P.split);
     return c;
