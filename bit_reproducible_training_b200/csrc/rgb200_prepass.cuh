@@ -112,12 +112,9 @@ struct KmajorOperand {
 // the forward GEMM of a linear layer needs one pre-pass launch.  `zero_word`, if not null, is cleared
 // by one thread (the workspace's status word, when no memset precedes this launch).
 template <int S, int TPR, int CHUNKS, bool VEC>
-__global__ void __launch_bounds__(PREPASS_THREADS)
-split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int blocks_first,
-                    int K, int Kp, int* zero_word) {
+__device__ __forceinline__ void split_kmajor_body(const KmajorOperand& first, const KmajorOperand& second, int blocks_first,
+                                                  int K, int Kp, int* zero_word) {
     __shared__ float red[PREPASS_THREADS / 32];
-    // the other operand's split, if launched behind this kernel with programmatic serialization, may start now
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int rows_per_cta = PREPASS_THREADS / TPR;
     if (zero_word && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *zero_word = 0;
     const bool is_first = (int)blockIdx.x < blocks_first;
@@ -185,6 +182,19 @@ split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int b
             store_quad<S>(v, q, plain_row(e), out, plane_stride, (size_t)k);
         }
     }
+}
+
+// Programmatic dependent launch: this kernel lets a kernel launched behind it with programmatic stream
+// serialization start early (the other operand's split, which does not depend on it), and, when it is itself
+// launched that way, does not complete before the kernel in front of it has: the ordinary launch that follows
+// (the MMA kernel) then finds both operands' planes complete.  Both instructions do nothing in an ordinary launch.
+template <int S, int TPR, int CHUNKS, bool VEC>
+__global__ void __launch_bounds__(PREPASS_THREADS)
+split_kmajor_kernel(const KmajorOperand first, const KmajorOperand second, int blocks_first,
+                    int K, int Kp, int* zero_word) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    split_kmajor_body<S, TPR, CHUNKS, VEC>(first, second, blocks_first, K, Kp, zero_word);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // Short rows (K <= 128, one padded k block per row; 16-byte aligned rows): a warp per row - or, for K <= 64, a

@@ -120,10 +120,9 @@ split_kstrided_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const fl
     const QuantScale q = quant_scale(e, S);
     const float limf = (float)q.lim;
     const bool plain = __all_sync(0xFFFFFFFFu, plain_row(e));
-    if (!arrived || r_glob >= R) return;
     const size_t plane_stride = (size_t)R * Kp;
     int8_t* out = planes + (size_t)b * S * plane_stride + (size_t)r_glob * Kp + k0;
-    for (int kk = g * 32; kk < nk; kk += G * 32) {
+    for (int kk = g * 32; arrived && r_glob < R && kk < nk; kk += G * 32) {
         const float* col = slab + (size_t)kk * W + r;
         uint32_t w[S][8];
 #pragma unroll
@@ -140,6 +139,9 @@ split_kstrided_cluster_kernel(const __grid_constant__ CUtensorMap tmap, const fl
             st_global_256(reinterpret_cast<uint32_t*>(out + p * plane_stride + kk),
                           w[p][0], w[p][1], w[p][2], w[p][3], w[p][4], w[p][5], w[p][6], w[p][7]);
     }
+    // launched behind the other operand's split with programmatic serialization, this grid must not complete before
+    // that one has (the MMA kernel is launched behind this grid); nothing to wait for in an ordinary launch
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace rgb200
