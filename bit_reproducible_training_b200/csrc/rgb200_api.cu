@@ -322,6 +322,12 @@ cudaError_t launch_cluster_split(const CUtensorMap& map, const float* given_max,
     return cudaLaunchKernelEx(&cfg, split_kstrided_cluster_kernel<S, W>, map, given_max, planes, expo, R, K, Kp, KC, status);
 }
 
+// Whether a k-strided operand of R rows (16-byte aligned base and batch stride taken for granted) takes the cluster form.
+bool cluster_split_fits(int R, int Kp) {
+    const int KC = ceil_div(ceil_div(Kp, KSC_CLUSTER), KSC_BOX_K) * KSC_BOX_K;
+    return R % 4 == 0 && (size_t)KC * 8 * 4 <= (size_t)KSC_MAX_SLAB_BYTES;
+}
+
 template <int S>
 bool try_cluster_split(const float* src, const float* given_max, int8_t* planes, int* expo, int R, int K, int Kp, int batch,
                        long long batch_stride, int* status, bool overlap, cudaStream_t st) {
@@ -1037,12 +1043,13 @@ int rgb200_host_gemm_create(int M, int N, int K, const rgb200_config* cfg, int b
         if ((e = plan_layout(b.rows, N, K, K, 1, *cfg, false, L)) != cudaSuccess) { host_gemm_free(h); return e; }
         h->layouts.push_back(L);
         h->ws_bytes = L.total > h->ws_bytes ? L.total : h->ws_bytes;
-        // launches per block: A's split (two kernels when A is stored k-strided), the MMA kernel, the K-range reduction
-        h->launches += (cfg->trans_a ? 2 : 1) + 1 + (L.use_partial_ws ? 1 : 0);
+        // launches per block: A's split (a k-strided operand that cannot take the cluster form needs two kernels),
+        // the MMA kernel, the K-range reduction
+        h->launches += (cfg->trans_a && !cluster_split_fits(b.rows, L.Kp) ? 2 : 1) + 1 + (L.use_partial_ws ? 1 : 0);
     }
-    // B's split, once per product: two kernels when B is stored k-strided, one when k-contiguous, and none
-    // extra when A is k-contiguous too (the first block's launch then splits both operands)
-    h->launches += cfg->trans_b ? (cfg->trans_a ? 1 : 0) : 2;
+    // B's split, once per product: one kernel, two when B is stored k-strided and cannot take the cluster form, and none
+    // extra when both operands are k-contiguous (the first block's launch then splits both)
+    h->launches += cfg->trans_b ? (cfg->trans_a ? 1 : 0) : (cluster_split_fits(N, h->layouts[0].Kp) ? 1 : 2);
     const size_t na = (size_t)M * K, nb = (size_t)K * N, nc = (size_t)M * N;
     if ((e = cudaMalloc(&h->dA, na * sizeof(float))) != cudaSuccess || (e = cudaMalloc(&h->dB, nb * sizeof(float))) != cudaSuccess ||
         (e = cudaMalloc(&h->dC, nc * sizeof(float))) != cudaSuccess || (e = cudaMalloc(&h->ws, h->ws_bytes)) != cudaSuccess ||

@@ -277,8 +277,9 @@ def test_host_buffer_pipeline_short_last_block_with_own_k_ranges():
     pipe = rg.HostGemm(M, N, K, rg.Config(), block_rows=512)
     pipe(hA, hB, hC)
     torch.cuda.synchronize()
-    # kernels per call: B's two pre-pass kernels once, A's split + MMA per block, one K-range reduction for the short block
-    assert pipe.blocks == 2 and pipe.launches == 2 + 2 + 3
+    # kernels per call: B's split once (one kernel: the cluster form), A's split + MMA per block, one K-range reduction
+    # for the short block
+    assert pipe.blocks == 2 and pipe.launches == 1 + 2 + 3
     assert np.array_equal(hC.numpy().view(np.uint32), want.view(np.uint32).reshape(-1))
 
 
