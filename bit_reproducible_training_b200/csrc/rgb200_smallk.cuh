@@ -231,22 +231,37 @@ gemm_i8_smallk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            uint32_t a_it = 0, b_it = 0;
+            uint32_t a_it = 0, b_it = 0, units = 0;      // A tiles requested, B tiles requested, units entered
             bool ok = true, new_row = true;
-            TileWalk w;
+            int in_unit = 0;
+            TileWalk w, wa;                               // wa: the unit whose A tile is requested next
             w.init(blockIdx.x, gridDim.x, P.n_tiles, P.m_tiles, P.batch);
+            wa = w;
+            auto load_a = [&]() {
+                const int ab = a_it & 1;
+                if (!mbar_wait(a_empty(ab), ((a_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY)) return false;
+                mbar_arrive_expect_tx(a_full(ab), Tr::A_BYTES);
+                tma_load_4d(a_base + ab * Tr::A_BYTES, &tmap_a, a_full(ab), 0, wa.m_blk * BLOCK_M, 0, wa.batch);
+                ++a_it;
+                wa.unit += wa.stride;
+                if (wa.valid()) wa.place();
+                return true;
+            };
             for (; w.valid(); ++b_it) {
                 if (new_row) {
-                    const int ab = a_it & 1;
-                    if (!(ok = mbar_wait(a_empty(ab), ((a_it >> 1) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
-                    mbar_arrive_expect_tx(a_full(ab), Tr::A_BYTES);
-                    tma_load_4d(a_base + ab * Tr::A_BYTES, &tmap_a, a_full(ab), 0, w.m_blk * BLOCK_M, 0, w.batch);
-                    ++a_it;
+                    if (a_it == units && !(ok = load_a())) break;      // not requested ahead (the first unit)
+                    ++units;
+                    in_unit = 0;
                 }
+                // The next unit's A tile is requested well before the MMA issuers get there: once this unit is as
+                // many tiles old as there are B stages, the unit before it is over and its buffer is free (a short
+                // unit asks at its last tile and may have to wait for that).
+                if (a_it == units && wa.valid() && (in_unit >= SK_B_STAGES || w.n_blk + 1 >= w.n_end) && !(ok = load_a())) break;
                 const int s = b_it % SK_B_STAGES;
                 if (!(ok = mbar_wait(b_empty(s), ((b_it / SK_B_STAGES) & 1u) ^ 1u, abort_flag, P.status, STATUS_WAIT_EMPTY))) break;
                 mbar_arrive_expect_tx(b_full(s), Tr::B_STAGE_BYTES);
                 tma_load_4d(b_base + s * Tr::B_STAGE_BYTES, &tmap_b, b_full(s), 0, w.n_blk * NT, 0, w.batch);
+                ++in_unit;
                 new_row = w.advance();
             }
             if (!ok) {
